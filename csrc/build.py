@@ -38,8 +38,27 @@ def _nvcc() -> str:
     raise RuntimeError("nvcc not found")
 
 
-def _sources() -> list[str]:
+# Named subsets of the translation units: a program that serves one family of models on a fresh checkout builds only
+# what that family launches (``build(unit_set=...)`` -> ops/libb200petals_<name>.so); the full library is every unit.
+UNIT_SETS = {
+    "layered": ["common", "gemm", "gemm_prefill", "elementwise", "sampling", "stream32", "gemm_simt", "latent_attention",
+                "moe"],
+}
+
+
+def _sources(unit_set: str | None = None) -> list[str]:
+    if unit_set is not None:
+        return [os.path.join(HERE, u + ".cu") for u in sorted(UNIT_SETS[unit_set])]
     return sorted(os.path.join(HERE, f) for f in os.listdir(HERE) if f.endswith(".cu"))
+
+
+def lib_path(unit_set: str | None = None) -> str:
+    return OUT_LIB if unit_set is None else OUT_LIB.replace(".so", f"_{unit_set}.so")
+
+
+def up_to_date(unit_set: str | None = None) -> bool:
+    """Is the library of this unit set present and not older than its sources and headers?"""
+    return not _newer(lib_path(unit_set), _sources(unit_set) + _headers())
 
 
 def _headers() -> list[str]:
@@ -56,18 +75,19 @@ def _newer(target: str, deps: list[str]) -> bool:
     return any(os.path.getmtime(d) > t for d in deps)
 
 
-def build(force: bool = False, verbose: bool = False, trace: bool = False) -> str:
+def build(force: bool = False, verbose: bool = False, trace: bool = False, unit_set: str | None = None) -> str:
     """trace=True builds the variant with the device-side event trace compiled in (csrc/trace.cuh) as
-    ops/libb200petals_trace.so; select it with B200_LIB (scripts/trace_decode.py does)."""
+    ops/libb200petals_trace.so; select it with B200_LIB (scripts/trace_decode.py does).
+    unit_set: one of UNIT_SETS, builds only those units into their own library file."""
     obj_dir = OBJ_DIR + ("_trace" if trace else "")
-    out_lib = OUT_LIB.replace(".so", "_trace.so") if trace else OUT_LIB
+    out_lib = OUT_LIB.replace(".so", "_trace.so") if trace else lib_path(unit_set)
     extra = ["-DB200_TRACE"] if trace else []
     os.makedirs(obj_dir, exist_ok=True)
     nvcc = _nvcc()
     headers = _headers()
     jobs = []
     objs = []
-    for src in _sources():
+    for src in _sources(unit_set):
         obj = os.path.join(obj_dir, os.path.basename(src)[:-3] + ".o")
         objs.append(obj)
         if force or _newer(obj, [src] + headers):
@@ -88,11 +108,13 @@ def build(force: bool = False, verbose: bool = False, trace: bool = False) -> st
                 if r.returncode != 0:
                     raise RuntimeError(f"nvcc failed for {cmd[-3]}")
     if jobs or force or _newer(out_lib, objs):
-        cmd = [nvcc, "-shared", "-o", out_lib, *objs]
+        tmp = f"{out_lib}.{os.getpid()}.tmp"          # (two first callers may build at once: link aside, then rename)
+        cmd = [nvcc, "-shared", "-o", tmp, *objs]
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
             sys.stderr.write(r.stdout + r.stderr)
             raise RuntimeError("link failed")
+        os.replace(tmp, out_lib)
     return out_lib
 
 
@@ -101,5 +123,6 @@ if __name__ == "__main__":
     ap.add_argument("--force", action="store_true")
     ap.add_argument("--verbose", action="store_true")
     ap.add_argument("--trace", action="store_true", help="build the event-trace variant (libb200petals_trace.so)")
+    ap.add_argument("--unit-set", choices=sorted(UNIT_SETS), help="build only this subset into its own library")
     a = ap.parse_args()
-    print(build(force=a.force, verbose=a.verbose, trace=a.trace))
+    print(build(force=a.force, verbose=a.verbose, trace=a.trace, unit_set=a.unit_set))

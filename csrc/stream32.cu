@@ -1,0 +1,128 @@
+// Elementwise kernels of designs that keep the residual stream in fp32: embedding gather to fp32, residual update
+// fused with the RMS norm that follows it, and the clamped gated unit of a feed-forward layer.
+#include "common.h"
+#include "ptx.cuh"
+
+namespace b200 {
+
+__device__ __forceinline__ float load_elem(const void* p, size_t i, int dtype) {
+    if (dtype == B200_F32) return static_cast<const float*>(p)[i];
+    return h16_to_float(static_cast<const uint16_t*>(p)[i], dtype == B200_BF16);
+}
+__device__ __forceinline__ void store_elem(void* p, size_t i, float v, int dtype) {
+    if (dtype == B200_F32)
+        static_cast<float*>(p)[i] = v;
+    else
+        static_cast<uint16_t*>(p)[i] = float_to_h16(v, dtype == B200_BF16);
+}
+
+// ------------------------------------------------------------------ embedding -> fp32
+__global__ void __launch_bounds__(128) embed_f32_kernel(const long long* __restrict__ ids, const void* __restrict__ table,
+                                                       int dtype, float* __restrict__ out, int T, int width, int ldo,
+                                                       int vocab) {
+    pdl_wait_prior_grid();
+    pdl_launch_dependents();
+    const int t = blockIdx.x;
+    if (t >= T) return;
+    long long id = ids[t];
+    id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);
+    for (int c = threadIdx.x; c < width; c += blockDim.x) out[(size_t)t * ldo + c] = load_elem(table, (size_t)id * width + c, dtype);
+}
+
+// ------------------------------------------------------------------ residual update + RMS norm
+// One block per token.  The updated row is kept in shared memory between the two passes.
+__global__ void __launch_bounds__(256) add_rms_norm_kernel(b200_add_norm_args a) {
+    extern __shared__ float row[];
+    __shared__ float red[8];
+    pdl_wait_prior_grid();
+    pdl_launch_dependents();
+    const int t = blockIdx.x;
+    float* x = a.x + (size_t)t * a.ldx;
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < a.width; c += blockDim.x) {
+        float v = x[c];
+        float add = 0.f;
+        bool any = false;
+        if (a.add_a) { add += a.add_a[(size_t)t * a.lda + c]; any = true; }
+        if (a.add_b) { add += a.add_b[(size_t)t * a.ldb + c]; any = true; }
+        if (a.pair_y) {
+            float m = 0.f;
+            for (int k = 0; k < a.top; ++k) {
+                const size_t p = (size_t)t * a.top + k;
+                const float y = a.pair_y[p * a.ldp + c];
+                m += a.pair_w ? a.pair_w[p] * y : y;
+            }
+            add += m;
+            any = true;
+        }
+        if (any) {
+            v += add;
+            x[c] = v;
+        }
+        row[c] = v;
+        ss += v * v;
+    }
+    if (!a.out) return;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    float tot = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) tot += red[w];
+    const float rstd = 1.0f / sqrtf(tot / (float)a.width + a.eps);
+    for (int c = threadIdx.x; c < a.width; c += blockDim.x)
+        store_elem(a.out, (size_t)t * a.ldo + c, row[c] * rstd * (a.gain_offset + a.gain[c]), a.out_dtype);
+}
+
+// ------------------------------------------------------------------ clamped gated unit
+__global__ void __launch_bounds__(256) glu_clamp_kernel(const float* __restrict__ gate, const float* __restrict__ up, int ld,
+                                                       void* __restrict__ act, int ldo, int out_dtype, int T, int ff,
+                                                       float limit, float alpha, float up_shift) {
+    pdl_wait_prior_grid();
+    pdl_launch_dependents();
+    const size_t n = (size_t)T * ff;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        const int t = (int)(i / ff), c = (int)(i - (size_t)t * ff);
+        float g = gate[(size_t)t * ld + c], u = up[(size_t)t * ld + c];
+        if (limit > 0.f) {
+            g = fminf(g, limit);
+            u = fminf(fmaxf(u, -limit), limit);
+        }
+        const float y = g / (1.0f + expf(-alpha * g)) * (u + up_shift);
+        store_elem(act, (size_t)t * ldo + c, y, out_dtype);
+    }
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" int b200_embed_f32(const void* ids, const void* table, int32_t table_dtype, float* out, int32_t T, int32_t width,
+                              int32_t ldo, int32_t vocab, int32_t pdl, void* stream) {
+    if (!ids || !table || !out || T <= 0 || width <= 0) return fail(B200_EINVAL, "b200_embed_f32: bad argument");
+    B200_CUDA_CHECK(launch(embed_f32_kernel, dim3(T), dim3(128), 0, static_cast<cudaStream_t>(stream), pdl != 0,
+                           static_cast<const long long*>(ids), table, table_dtype, out, T, width, ldo, vocab));
+    return B200_OK;
+}
+
+extern "C" int b200_add_rms_norm(const b200_add_norm_args* a, void* stream) {
+    if (!a || !a->x || a->T <= 0 || a->width <= 0) return fail(B200_EINVAL, "b200_add_rms_norm: bad argument");
+    if (a->out && !a->gain) return fail(B200_EINVAL, "b200_add_rms_norm: out without gain");
+    const size_t smem = (size_t)a->width * sizeof(float);
+    if (smem > 200 * 1024) return fail(B200_ELIMIT, "b200_add_rms_norm: width %d exceeds the row buffer", a->width);
+    if (smem > 48 * 1024)
+        B200_CUDA_CHECK(cudaFuncSetAttribute(add_rms_norm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    B200_CUDA_CHECK(launch(add_rms_norm_kernel, dim3(a->T), dim3(256), smem, static_cast<cudaStream_t>(stream), a->pdl != 0, *a));
+    return B200_OK;
+}
+
+extern "C" int b200_glu_clamp(const float* gate, const float* up, int32_t ld, void* act, int32_t ldo, int32_t out_dtype,
+                              int32_t T, int32_t ff, float limit, float alpha, float up_shift, int32_t pdl, void* stream) {
+    if (!gate || !up || !act || T <= 0 || ff <= 0) return fail(B200_EINVAL, "b200_glu_clamp: bad argument");
+    const size_t n = (size_t)T * ff;
+    const int blocks = (int)((n + 255) / 256 < 4096 ? (n + 255) / 256 : 4096);
+    B200_CUDA_CHECK(launch(glu_clamp_kernel, dim3(blocks), dim3(256), 0, static_cast<cudaStream_t>(stream), pdl != 0, gate, up,
+                           ld, act, ldo, out_dtype, T, ff, limit, alpha, up_shift));
+    return B200_OK;
+}

@@ -1,4 +1,4 @@
-"""Architecture descriptions for the two supported families (Llama, GPT-2).
+"""Architecture descriptions for the supported families (Llama, GPT-2, and the layer-list design Gigezen).
 
 The reference accepts any HF model name but only runs Llama-family models
 (src/llama_partition.py:81-83) while advertising GPT-2 (README / run_all.py
@@ -83,7 +83,14 @@ class ModelConfig:
                     activation_function="gelu_new")
 
 
-def from_hf_dict(d: Dict[str, Any], name: str = "") -> ModelConfig:
+def from_hf_dict(d: Dict[str, Any], name: str = ""):
+    """The configuration object of a ``config.json``: the model registry.  Families with uniform layers are a
+    :class:`ModelConfig`; layer-list designs bring their own class (same ``family`` / ``n_layers`` / ``hidden`` /
+    ``vocab`` surface)."""
+    if str(d.get("architecture", "")).lower() == "gigezen":
+        from . import gigezen
+
+        return gigezen.from_config_dict(d, name)
     mt = str(d.get("model_type", "")).lower()
     if mt == "gpt2":
         h = int(d["n_embd"])
@@ -107,7 +114,7 @@ def from_hf_dict(d: Dict[str, Any], name: str = "") -> ModelConfig:
                            int(d.get("max_position_embeddings", 4096)),
                            bool(d.get("tie_word_embeddings", False)), name,
                            d.get("bos_token_id"), eos)
-    raise ValueError(f"unsupported model_type {mt!r} (supported: gpt2, llama, mistral)")
+    raise ValueError(f"unsupported model_type {mt!r} (supported: gpt2, llama, mistral; architecture: Gigezen)")
 
 
 def _llama(name, L, H, nh, nkv, I, V, theta=10000.0, maxpos=4096, scaling=None, eps=1e-5):
@@ -149,7 +156,13 @@ _ALIASES = {
 }
 
 
-def resolve_config(model: str) -> ModelConfig:
+def _presets() -> Dict[str, Any]:
+    from . import gigezen
+
+    return {**PRESETS, **gigezen.PRESETS}
+
+
+def resolve_config(model: str):
     """``model`` is a local HF directory (config.json), a preset, or a known hub id."""
     if os.path.isdir(model) and os.path.exists(os.path.join(model, "config.json")):
         with open(os.path.join(model, "config.json")) as f:
@@ -158,10 +171,11 @@ def resolve_config(model: str) -> ModelConfig:
     if key.startswith("random:"):
         key = key[len("random:"):]
     key = _ALIASES.get(key, key)
-    if key in PRESETS:
-        return PRESETS[key]
+    presets = _presets()
+    if key in presets:
+        return presets[key]
     raise ValueError(
-        f"unknown model {model!r}: pass a local HF checkpoint directory or one of {sorted(PRESETS)} "
+        f"unknown model {model!r}: pass a local HF checkpoint directory or one of {sorted(presets)} "
         "(no network: hub downloads are unavailable)"
     )
 

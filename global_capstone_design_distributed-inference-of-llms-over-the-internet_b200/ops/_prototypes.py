@@ -36,7 +36,44 @@ class HopArgs(C.Structure):
                 ("depth", i32), ("t_max", i32), ("pairs_per_token", i32), ("timeout_ms", i32), ("pdl", i32)]
 
 
+class AddNormArgs(C.Structure):
+    """Mirror of ``b200_add_norm_args``."""
+
+    _fields_ = [("x", vp), ("add_a", vp), ("add_b", vp), ("pair_y", vp), ("pair_w", vp), ("gain", vp), ("out", vp),
+                ("T", i32), ("width", i32), ("ldx", i32), ("lda", i32), ("ldb", i32), ("ldp", i32), ("top", i32),
+                ("ldo", i32), ("out_dtype", i32), ("eps", f32), ("gain_offset", f32), ("pdl", i32)]
+
+
+class SimtGemmArgs(C.Structure):
+    """Mirror of ``b200_simt_gemm_args``."""
+
+    _fields_ = [("x", vp), ("w", vp), ("w2", vp), ("out", vp), ("row_src", vp), ("row_dst", vp), ("group_off", vp),
+                ("row_scale", vp),
+                ("T", i32), ("N", i32), ("K", i32), ("ldx", i32), ("ldw", i32), ("ldo", i32),
+                ("x_dtype", i32), ("w_dtype", i32), ("out_dtype", i32), ("batch", i32), ("groups", i32),
+                ("x_bs", i64), ("w_bs", i64), ("o_bs", i64), ("w_gs", i64), ("pdl", i32), ("reserved", i32)]
+
+
+class LatentArgs(C.Structure):
+    """Mirror of ``b200_latent_args``."""
+
+    _fields_ = [("proj", vp), ("ldp", i32), ("q_off", i32), ("kv_off", i32), ("c_gain", vp), ("inv_freq", vp),
+                ("cache", vp), ("kv_ptrs", vp), ("pos", vp), ("kv_ptr_stride", i32), ("pos0", i32),
+                ("T", i32), ("heads", i32), ("dim", i32), ("rot", i32), ("rot_dims", i32), ("kv_rank", i32),
+                ("row_elems", i32), ("cache_dtype", i32), ("eps", f32),
+                ("q_abs", vp), ("out", vp), ("ldqa", i32), ("ldout", i32), ("window", i32), ("scale", f32),
+                ("pdl", i32), ("reserved", i32)]
+
+
 PROTOTYPES = [
+    ("b200_embed_f32", [vp, vp, i32, vp, i32, i32, i32, i32, i32, vp], C.c_int),
+    ("b200_add_rms_norm", [C.POINTER(AddNormArgs), vp], C.c_int),
+    ("b200_glu_clamp", [vp, vp, i32, vp, i32, i32, i32, i32, f32, f32, f32, i32, vp], C.c_int),
+    ("b200_gemm_simt", [C.POINTER(SimtGemmArgs), vp], C.c_int),
+    ("b200_latent_rope_append", [C.POINTER(LatentArgs), vp], C.c_int),
+    ("b200_latent_attn", [C.POINTER(LatentArgs), vp], C.c_int),
+    ("b200_moe_route", [vp, i32, i32, i32, i32, i32, i32, i32, vp, vp, i32, vp], C.c_int),
+    ("b200_moe_plan", [vp, i32, i32, i32, vp, vp, vp, i32, vp], C.c_int),
     ("b200_hop_ring_bytes", [i32, i32, i32], i64),
     ("b200_hop_send", [C.POINTER(HopArgs), vp], C.c_int),
     ("b200_hop_recv", [C.POINTER(HopArgs), vp], C.c_int),

@@ -111,23 +111,24 @@ class PipelineEngine:
                                      kv_capacity=kv_capacity, max_batch=max_sessions, max_chunk=max_chunk,
                                      use_graphs=use_graphs, head_rows=head_rows, attn_splits=attn_splits)
         elif self.backend == "native":
-            from ..runtime.native_span import NativeSpan
+            from ..runtime.layered_span import make_span
 
-            self.span = NativeSpan(self.cfg, w, self.device, dtype, kv_capacity=kv_capacity,
-                                   max_batch=max_sessions, max_chunk=max_chunk, use_graphs=use_graphs,
-                                   weight_format=weight_format, head_rows=head_rows, attn_splits=attn_splits)
+            self.span = make_span(self.cfg, w, self.device, dtype, kv_capacity=kv_capacity,
+                                  max_batch=max_sessions, max_chunk=max_chunk, use_graphs=use_graphs,
+                                  weight_format=weight_format, head_rows=head_rows, attn_splits=attn_splits)
         else:
             from ..models.torch_ref import TorchSpan
 
             self.span = TorchSpan(self.cfg, w, self.device, dtype)
         if self.tp > 1 and self.backend != "native":
             raise ValueError("tensor-parallel spans need the native (CUDA) backend")
-        self.kv = KVCacheManager(self.end - self.start, self.cfg.n_kv_heads // self.tp, self.cfg.head_dim, dtype,
-                                 self.device, default_max_length=kv_capacity)
+        self.kv = KVCacheManager.for_span(self.cfg, self.start, self.end, dtype, self.device, tp=self.tp,
+                                          default_max_length=kv_capacity)
         self.sessions: List[SessionKV] = []
         H = self.cfg.hidden
         # per-slot staging buffers: [0] = received from the previous stage, [1] = sent to the next
-        self._hid = torch.empty(2, max_sessions, H, dtype=dtype, device=self.device)
+        self.hidden_dtype = getattr(self.span, "hidden_dtype", dtype)     # (fp32 for designs with an fp32 residual stream)
+        self._hid = torch.empty(2, max_sessions, H, dtype=self.hidden_dtype, device=self.device)
         self._tok = torch.zeros(max_sessions, dtype=torch.int64, device=self.device)
         self._tok_send = torch.zeros(max_sessions, dtype=torch.int64, device=self.device)
         # Hidden states flow on the default group, token ids return on a second communicator:
@@ -381,7 +382,7 @@ class PipelineEngine:
         out = None
         recv_next = None
         if not self.is_first:
-            buf = torch.empty(chunks[0][1], H, dtype=self.dtype, device=self.device)
+            buf = torch.empty(chunks[0][1], H, dtype=self.hidden_dtype, device=self.device)
             recv_next = (buf, dist.irecv(buf, self._g(self.rank - 1)))
         for ci, (c0, n) in enumerate(chunks):
             h = None
@@ -389,7 +390,7 @@ class PipelineEngine:
                 h, work = recv_next
                 work.wait()
                 if ci + 1 < len(chunks):   # post the next receive before computing this chunk
-                    nb = torch.empty(chunks[ci + 1][1], H, dtype=self.dtype, device=self.device)
+                    nb = torch.empty(chunks[ci + 1][1], H, dtype=self.hidden_dtype, device=self.device)
                     recv_next = (nb, dist.irecv(nb, self._g(self.rank - 1)))
             out = self._stage_prefill(kv, ids_dev[c0:c0 + n] if self.is_first else None, h)
             if not self.is_last:

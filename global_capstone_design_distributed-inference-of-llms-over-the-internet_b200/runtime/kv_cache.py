@@ -25,7 +25,7 @@ from .memory_cache import AllocationFailed, MemoryCache, TensorDescriptor  # noq
 @dataclass
 class SessionKV:
     session_id: str
-    data: torch.Tensor            # [n_layers, 2, n_kv, max_len, head_dim]
+    data: torch.Tensor            # [n_layers, planes, n_kv, max_len, head_dim] (planes: K and V, or 1 for latent rows)
     max_len: int
     length: int = 0               # tokens cached so far
     last_used: float = field(default_factory=time.monotonic)
@@ -42,6 +42,11 @@ class SessionKV:
     def v(self, layer: int) -> torch.Tensor:
         return self.data[layer, 1]
 
+    def rows(self, slot: int) -> torch.Tensor:
+        """[max_len, row] rows of cache slot ``slot`` of a one-plane layout (latent attention: one row per token
+        shared by all heads; a slot is a cache-OWNING layer, layers that read another layer's cache have none)."""
+        return self.data[slot, 0, 0]
+
     def rollback(self, position: int) -> None:
         if not 0 <= position <= self.length:
             raise ValueError(f"cannot roll session back to {position} (length {self.length})")
@@ -54,8 +59,8 @@ class SessionKV:
 class KVCacheManager:
     def __init__(self, n_layers: int, n_kv_heads: int, head_dim: int, dtype: torch.dtype, device,
                  max_tokens: Optional[int] = None, default_max_length: int = 2048, session_ttl: float = 600.0,
-                 alloc_timeout: float = 0.0):
-        self.n_layers, self.n_kv, self.head_dim = n_layers, n_kv_heads, head_dim
+                 alloc_timeout: float = 0.0, planes: int = 2):
+        self.n_layers, self.n_kv, self.head_dim, self.planes = n_layers, n_kv_heads, head_dim, int(planes)
         self.dtype, self.device = dtype, torch.device(device)
         self.max_tokens = max_tokens              # None = unlimited
         self.default_max_length = default_max_length
@@ -65,6 +70,14 @@ class KVCacheManager:
         self._lock = threading.Lock()
         # every session buffer is carved from this byte budget; waiters are woken when a session closes
         self.cache = MemoryCache(None if max_tokens is None else max_tokens * self.bytes_per_token(), alloc_timeout)
+
+    @classmethod
+    def for_span(cls, cfg, start: int, end: int, dtype: torch.dtype, device, tp: int = 1, **kw) -> "KVCacheManager":
+        """The manager whose sessions fit blocks [start, end) of ``cfg``: K and V planes per block and kv head for the
+        uniform families, one plane of latent rows per cache-owning layer for layer-list designs."""
+        if getattr(cfg, "family", "") == "gigezen":
+            return cls(max(1, len(cfg.cache_layers(start, end))), 1, cfg.cache_row(start, end), dtype, device, planes=1, **kw)
+        return cls(end - start, cfg.n_kv_heads // tp, cfg.head_dim, dtype, device, **kw)
 
     # ---- accounting
     @property
@@ -76,7 +89,7 @@ class KVCacheManager:
         return None if self.max_tokens is None else self.max_tokens - self.tokens_used
 
     def bytes_per_token(self) -> int:
-        return 2 * self.n_layers * self.n_kv * self.head_dim * torch.empty((), dtype=self.dtype).element_size()
+        return self.planes * self.n_layers * self.n_kv * self.head_dim * torch.empty((), dtype=self.dtype).element_size()
 
     # ---- lifecycle
     def get(self, session_id: str) -> Optional[SessionKV]:
@@ -109,7 +122,7 @@ class KVCacheManager:
             self._drop(session_id)
             if self.max_tokens is not None and self.tokens_used + max_length > self.max_tokens:
                 self._evict_lru_until(max_length)
-        desc = TensorDescriptor((self.n_layers, 2, self.n_kv, max_length, self.head_dim), self.dtype, self.device)
+        desc = TensorDescriptor((self.n_layers, self.planes, self.n_kv, max_length, self.head_dim), self.dtype, self.device)
         stack = contextlib.ExitStack()
         try:
             handles = stack.enter_context(self.cache.allocate_cache(desc, timeout=timeout))   # may block (no lock held)

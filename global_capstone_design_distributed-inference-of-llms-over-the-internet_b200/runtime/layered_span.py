@@ -1,0 +1,374 @@
+"""B200 execution of a span of a layer-list design (first user: Gigezen) with an fp32 residual stream.
+
+``LayeredSpan`` plugs into everything a :class:`NativeSpan` plugs into - sessions of the cache manager, the
+captured decode step with its staged positions / cache pointers, the device sampler, the pipeline engine and the
+served stages - and replaces what is specific to the uniform families: the weights it packs, the kernels of a layer
+and the head.  Per layer (T tokens of any mix of sessions):
+
+    hn    = rms_norm(x += previous layer's outputs) * (1 + g)        b200_add_rms_norm      fp32 -> 16-bit
+    proj  = hn . [Wq | Wdkv | Wrouter | Wgate | Wup]^T               tcgen05 GEMM, fp32 out (one launch)
+    rotary on q / shared key part, latent norm, cache append         b200_latent_rope_append
+    q_abs = q_unrotated pulled through W_uk, per head                b200_gemm_simt (batched over heads)
+    o_lat = softmax(window scores) . latents                         b200_latent_attn
+    cat   = [ W_uv o_lat per head | clamped gated unit ]             b200_gemm_simt (batched) + b200_glu_clamp
+    y     = cat . [Wo | Wdown]^T                                     tcgen05 GEMM, fp32 out: mixer + dense ff in one
+    experts (mixture layers): route, plan, grouped gate/up and down  b200_moe_* + b200_gemm_simt (grouped)
+
+``dtype=torch.float32`` runs the same step with every product in true fp32 (``b200_gemm_simt`` instead of the
+tensor-core GEMM) and an fp32 cache.
+"""
+from __future__ import annotations
+
+import os
+from typing import Dict, List, Optional, Sequence
+
+import torch
+
+from ..models import gigezen as Z
+from ..ops import elementwise as E
+from ..ops import gemm as G
+from ..ops import layered as L
+from ..ops import packing
+from .kv_cache import SessionKV
+from .native_span import MAX_DECODE_BATCH, NativeSpan, _pdl_default
+
+
+def _pad64(n: int) -> int:
+    return (n + 63) // 64 * 64
+
+
+class _Linear:
+    """One weight in the form the span's mode multiplies with: packed tiles (16-bit) or the dense fp32 matrix."""
+
+    def __init__(self, w: torch.Tensor, exact: bool):
+        self.n, self.k = w.shape
+        self.k_padded = self.k if exact else _pad64(self.k)
+        self.dense = w.contiguous() if exact else None
+        self.packed = None if exact else packing.pack_weight(w)
+        self.nbytes = w.numel() * w.element_size()
+
+
+class LayeredSpan(NativeSpan):
+    hidden_dtype = torch.float32        # what enters and leaves the span between pipeline stages
+
+    def __init__(self, cfg: Z.GigezenConfig, weights: Dict[str, object], device, dtype: torch.dtype, *,
+                 kv_capacity: int = 2048, max_batch: int = 8, max_chunk: int = 512, use_graphs: bool = True,
+                 pdl: Optional[bool] = None, free_source_weights: bool = True, weight_format: str = "native",
+                 head_rows: Optional[tuple] = None, attn_splits: int = 0, streamed_layers: int = 0):
+        if dtype not in (torch.bfloat16, torch.float16, torch.float32):
+            raise ValueError("a layered span runs in bfloat16 / float16 (tensor-core products) or float32 (all fp32)")
+        if weight_format != "native" or head_rows is not None or streamed_layers:
+            raise NotImplementedError("layered spans: 16-bit or fp32 weights, whole head, resident layers")
+        self.cfg, self.device, self.dtype = cfg, torch.device(device), dtype
+        self.exact = dtype == torch.float32
+        self.kv_capacity, self.max_batch, self.max_chunk = kv_capacity, min(max_batch, MAX_DECODE_BATCH), max_chunk
+        self.use_graphs = use_graphs
+        self.weight_format = "native"
+        self.pdl = _pdl_default() if pdl is None else pdl
+        self.l2_prefetch_mb = None
+        self.streamed_layers = 0
+        self._prefill_plans = {}
+        self.has_embed = bool(weights.get("has_embed", False))
+        self.has_head = bool(weights.get("has_head", "lm_head" in weights))
+        self.start = int(weights.get("start", 0))
+        W = cfg.hidden
+        ex = self.exact
+        specs = cfg.layers[self.start:self.start + len(weights["layers"])]    # type: ignore[arg-type]
+        cfg.check_span(self.start, self.start + len(specs))
+        slots = {a: s for s, a in enumerate(cfg.cache_layers(self.start, self.start + len(specs)))}
+        self.n_slots = max(1, len(slots))
+        self.row_elems = cfg.cache_row(self.start, self.start + len(specs))
+        with torch.cuda.device(self.device):
+            self.layers: List[dict] = []
+            self._inv_freq: Dict[tuple, torch.Tensor] = {}
+            for i, (S, Lw) in enumerate(zip(specs, weights["layers"])):   # type: ignore[arg-type]
+                m = S.mixer
+                parts, P = [Lw["q_w"]], {"spec": S, "norm_w": Lw["norm1_w"], "q_off": 0, "kv_off": -1}
+                n = m.q_size
+                if m.owns_cache:
+                    P["kv_off"], P["c_gain"] = n, Lw["dkv_norm_w"]
+                    parts.append(Lw["dkv_w"])
+                    n += m.row
+                P["slot"] = slots[self.start + i if m.owns_cache else m.kv_from]
+                if isinstance(S.mlp, Z.MoESpec):
+                    P["r_off"] = n
+                    parts.append(Lw["router_w"])
+                    n += S.mlp.experts
+                    P["e_gate"], P["e_up"], P["e_down"] = Lw["e_gate"], Lw["e_up"], Lw["e_down"]
+                elif isinstance(S.mlp, Z.GatedMLPSpec):
+                    P["g_off"], P["u_off"] = n, n + S.mlp.ff
+                    parts += [Lw["gate_w"], Lw["up_w"]]
+                    n += 2 * S.mlp.ff
+                P["proj"] = _Linear(torch.cat(parts, 0), ex)
+                hv = m.heads * m.vdim
+                dense = isinstance(S.mlp, Z.GatedMLPSpec)
+                P["out"] = _Linear(torch.cat([Lw["o_w"], Lw["down_w"]], 1) if dense else Lw["o_w"], ex)
+                P["ukT"] = Lw["uk_w"].view(m.heads, m.dim, m.kv_rank).transpose(1, 2).contiguous()     # [H, R, dim]
+                P["uv"] = Lw["uv_w"].view(m.heads, m.vdim, m.kv_rank).contiguous()                     # [H, vdim, R]
+                key = (m.rope_base, m.rope_dims)
+                if key not in self._inv_freq:
+                    j = torch.arange(m.rope_dims // 2, dtype=torch.float64)
+                    self._inv_freq[key] = (torch.tensor(m.rope_base, dtype=torch.float64) ** (-2.0 * j / m.rope_dims)).to(self.device)
+                P["inv_freq"] = self._inv_freq[key]
+                P["hv"] = hv
+                self.layers.append(P)
+                if free_source_weights:
+                    for k in ("q_w", "dkv_w", "router_w", "gate_w", "up_w", "o_w", "down_w", "uk_w"):
+                        Lw.pop(k, None)
+            self.embed_w = weights.get("embed") if self.has_embed else None
+            self.pos_embed_w = None
+            self.head_lo, self.head_hi = 0, cfg.vocab
+            if self.has_head:
+                self.final_norm_w = weights["final_norm_w"]
+                self.lm_head = _Linear(weights["lm_head"], ex)       # type: ignore[arg-type]
+            Tm = max(self.max_chunk, self.max_batch)
+            adt = dtype                                             # element type of GEMM inputs
+            f32 = lambda *s: torch.zeros(*s, dtype=torch.float32, device=self.device)  # noqa: E731
+            act = lambda *s: torch.zeros(*s, dtype=adt, device=self.device)  # noqa: E731
+            mx = lambda f: max([f(P) for P in self.layers] or [1])  # noqa: E731
+            self.h_a = f32(Tm, W)
+            self.h_b = self.h_a                                      # (one stream buffer: layers update it in place)
+            self.hn = act(Tm, _pad64(W))
+            self.proj = f32(Tm, mx(lambda P: P["proj"].n))
+            self.qa = f32(Tm, mx(lambda P: P["spec"].mixer.heads * P["spec"].mixer.kv_rank))
+            self.ol = torch.zeros_like(self.qa)
+            self.cat = act(Tm, mx(lambda P: _pad64(P["out"].k)))
+            self.y = f32(Tm, W)
+            moe = [P["spec"].mlp for P in self.layers if isinstance(P["spec"].mlp, Z.MoESpec)]
+            if moe:
+                top, ne, ffe = max(e.top for e in moe), max(e.experts for e in moe), max(e.ff for e in moe)
+                self.moe_ids = torch.zeros(Tm, top, dtype=torch.int32, device=self.device)
+                self.moe_w = f32(Tm, top)
+                self.moe_off = torch.zeros(ne + 1, dtype=torch.int32, device=self.device)
+                self.moe_row_pair = torch.zeros(Tm * top, dtype=torch.int32, device=self.device)
+                self.moe_row_token = torch.zeros(Tm * top, dtype=torch.int32, device=self.device)
+                self.moe_act = f32(Tm * top, ffe)
+                self.moe_y = f32(Tm * top, W)
+            self.ids_in = torch.zeros(Tm, dtype=torch.int64, device=self.device)
+            self.ws = None if ex else G.GemmWorkspace.create(self.device, Tm)
+            self._make_stage_buffers(self.n_slots)
+            self.sampler = None
+            self._seq_host = 0
+            self.chain_tokens = 0
+            self._ptr_tables = {}
+            if self.has_head:
+                self.head_rows_max = max(self.max_batch, 32)
+                self.logits = f32(self.head_rows_max, cfg.vocab)
+                self.ids_out = torch.zeros(self.head_rows_max, dtype=torch.int64, device=self.device)
+                self.argmax_ws = E.ArgmaxWorkspace(self.device, self.head_rows_max)
+        self._graphs = {}
+        self._ptr_key = None
+        self.kernel_launches = 0
+        self._launches_per_graph = {}
+        self._pending = None
+
+    # ------------------------------------------------------------------ framework hooks
+    def _cache_slots(self) -> int:
+        return self.n_slots
+
+    def subspan(self, a: int, b: int):
+        if (a, b) == (0, len(self.layers)):
+            return self
+        raise NotImplementedError("sub-spans of a layered span (cache slots are shared between its layers)")
+
+    def weight_bytes(self) -> int:
+        n = 0
+        for P in self.layers:
+            n += P["proj"].nbytes + P["out"].nbytes + sum(P[k].numel() * P[k].element_size() for k in ("ukT", "uv"))
+            if "e_gate" in P:
+                n += sum(P[k].numel() * P[k].element_size() for k in ("e_gate", "e_up", "e_down"))
+        if self.has_head:
+            n += self.lm_head.nbytes
+        return n
+
+    # ------------------------------------------------------------------ pieces
+    def _linear(self, x: torch.Tensor, w: _Linear, out: torch.Tensor) -> torch.Tensor:
+        """out (fp32 [T, >= n] view) = x[:, :k] . W^T"""
+        T = x.shape[0]
+        if self.exact:
+            L.gemm_simt(x, w.dense, out, T=T, N=w.n, K=w.k, pdl=self.pdl)
+        else:
+            G.linear(x[:, :w.k_padded], w.packed, out=out[:, :w.n], out_fp32=True, workspace=self.ws, pdl=self.pdl)
+        self._count()
+        return out
+
+    def _embed(self, T: int, pos0: int, use_pos_buffer: bool) -> torch.Tensor:
+        h = self.h_a[:T]
+        L.embed_f32(self.ids_in[:T], self.embed_w, h, pdl=self.pdl)
+        self._count()
+        return h
+
+    def _flush(self, x: torch.Tensor, gain: Optional[torch.Tensor], out: Optional[torch.Tensor]) -> None:
+        """Adds what the previous layer left pending to the stream and (optionally) norms the result."""
+        pend, self._pending = self._pending or {}, None
+        if not pend and out is None:
+            return
+        L.add_rms_norm(x, gain, out, self.cfg.norm_eps, Z.NORM_GAIN_OFFSET, pdl=self.pdl, **pend)
+        self._count()
+
+    def _layer(self, T: int, x: torch.Tensor, P: dict, where: dict) -> None:
+        S, pdl = P["spec"], self.pdl
+        m = S.mixer
+        W = self.cfg.hidden
+        hn, proj, cat = self.hn[:T], self.proj[:T], self.cat[:T]
+        self._flush(x, P["norm_w"], hn[:, :W])
+        self._linear(hn, P["proj"], proj)
+        common = dict(heads=m.heads, dim=m.dim, rot=m.rot_dim, rot_dims=m.rope_dims, kv_rank=m.kv_rank,
+                      row_elems=self.row_elems, cache_dtype=self.dtype, eps=self.cfg.norm_eps, T=T, pdl=pdl)
+        if "kv" in where:      # one session: rows of its cache slot, consecutive positions
+            common.update(cache=where["kv"].rows(P["slot"]), pos0=where["pos0"])
+        else:                  # a batch of sessions: staged pointer table and positions
+            common.update(kv_ptrs=self.kv_ptrs[P["slot"]], kv_ptr_stride=2, pos=self.pos)
+        a = L.latent_args(proj, P["q_off"], P["kv_off"], P.get("c_gain"), P["inv_freq"], q_abs=self.qa, out=self.ol,
+                          window=m.window, scale=m.scale, **common)
+        a.ldqa = a.ldout = m.heads * m.kv_rank
+        L.latent_rope_append(a)
+        hd = m.dim + m.rot_dim
+        L.gemm_simt(proj[:, P["q_off"]:], P["ukT"], self.qa, T=T, N=m.kv_rank, K=m.dim, ldx=proj.stride(0), ldw=m.dim,
+                    ldo=m.heads * m.kv_rank, batch=m.heads, x_bs=hd, w_bs=m.kv_rank * m.dim, o_bs=m.kv_rank, pdl=pdl)
+        L.latent_attn(a)
+        L.gemm_simt(self.ol, P["uv"], cat, T=T, N=m.vdim, K=m.kv_rank, ldx=m.heads * m.kv_rank, ldw=m.kv_rank,
+                    ldo=cat.stride(0), batch=m.heads, x_bs=m.kv_rank, w_bs=m.vdim * m.kv_rank, o_bs=m.vdim, pdl=pdl)
+        self._count(4)
+        if isinstance(S.mlp, Z.GatedMLPSpec):
+            ff = S.mlp.ff
+            L.glu_clamp(proj[:, P["g_off"]:P["g_off"] + ff], proj[:, P["u_off"]:P["u_off"] + ff], cat[:, P["hv"]:],
+                        S.mlp.limit, Z.DENSE_GATE_ALPHA, Z.DENSE_UP_SHIFT, pdl=pdl)
+            self._count()
+        self._linear(cat, P["out"], self.y[:T])
+        self._pending = dict(add_a=self.y[:T])
+        if isinstance(S.mlp, Z.MoESpec):
+            e = S.mlp
+            n = T * e.top
+            ids, wts = self.moe_ids[:T, :e.top], self.moe_w[:T, :e.top]
+            if e.top != self.moe_ids.shape[1]:
+                ids, wts = self.moe_ids.view(-1)[:n].view(T, e.top), self.moe_w.view(-1)[:n].view(T, e.top)
+            L.moe_route(proj[:, P["r_off"]:P["r_off"] + e.experts], e.experts, e.groups, e.keep, e.top, ids, wts, pdl=pdl)
+            L.moe_plan(ids, T, e.top, e.experts, self.moe_off, self.moe_row_pair, self.moe_row_token, pdl=pdl)
+            grouped = dict(group_off=self.moe_off, groups=e.experts, T=n, pdl=pdl)
+            L.gemm_simt(hn, P["e_gate"], self.moe_act, w2=P["e_up"], N=e.ff, K=W, ldw=W, w_gs=e.ff * W,
+                        row_src=self.moe_row_token, **grouped)
+            L.gemm_simt(self.moe_act, P["e_down"], self.moe_y, N=W, K=e.ff, ldw=e.ff, w_gs=W * e.ff,
+                        row_dst=self.moe_row_pair, **grouped)
+            self._pending.update(pair_y=self.moe_y, pair_w=wts, top=e.top)
+            self._count(4)
+
+    def _run_layers(self, T: int, x: torch.Tensor, where: dict, norm_out: bool = False) -> torch.Tensor:
+        self._pending = None
+        for P in self.layers:
+            self._layer(T, x, P, where)
+        if norm_out and self.has_head:     # every row goes to the head: fold the final norm into the last update
+            self._flush(x, self.final_norm_w, self.hn[:T, :self.cfg.hidden])
+            self._normed = True
+        else:
+            self._flush(x, None, None)
+            self._normed = False
+        return x
+
+    def _decode_layers(self, T: int, h: torch.Tensor, with_head: bool = False) -> torch.Tensor:
+        self._head_done = False
+        return self._run_layers(T, h, {}, norm_out=with_head)
+
+    def _head(self, h_rows: torch.Tensor, greedy, out_ids: Optional[torch.Tensor] = None, init_pair=None, out_pair=None,
+              gemm_done: bool = False, row_index: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """h_rows: fp32 [B, W] rows of the stream -> logits [B, V] fp32 (and ids_out when greedy / sampling)."""
+        B, W = h_rows.shape
+        assert B <= self.head_rows_max and init_pair is None and out_pair is None
+        hn = self.hn[:B]
+        if not (getattr(self, "_normed", False) and h_rows.data_ptr() == self.h_a.data_ptr()):
+            L.add_rms_norm(h_rows, self.final_norm_w, hn[:, :W], self.cfg.norm_eps, Z.NORM_GAIN_OFFSET, pdl=self.pdl)
+            self._count()
+        self._normed = False
+        logits = self.logits[:B]
+        self._linear(hn, self.lm_head, logits)
+        if greedy == "sample":
+            assert self.sampler is not None, "sampling needs enable_sampling()"
+            idx = self.samp_idx[:B] if row_index is None else row_index
+            self.sampler.sample(logits, idx, self.ids_out[:B] if out_ids is None else out_ids, pdl=self.pdl)
+            self._count()
+        elif greedy:
+            E.argmax(logits, self.ids_out[:B] if out_ids is None else out_ids, self.argmax_ws, pdl=self.pdl)
+            self._count()
+        return logits
+
+    # ------------------------------------------------------------------ prefill
+    def prefill(self, kv: SessionKV, h_in: Optional[torch.Tensor] = None, ids: Optional[torch.Tensor] = None,
+                pos0: Optional[int] = None, greedy=True, logits_at: Optional[Sequence[int]] = None):
+        """Append T tokens of one session (chunked to ``max_chunk``).
+
+        Returns the stream [T, W] (fp32, new tensor) on a span without a head, else ``(logits, ids_out)`` of the last
+        position - or, with ``logits_at`` (indices into this call's tokens), a new [len(logits_at), V] fp32 tensor
+        with the logits at those positions and the arg-max ids beside it."""
+        self._prestaged = None
+        pos0 = kv.length if pos0 is None else pos0
+        T = ids.shape[0] if h_in is None else h_in.shape[0]
+        if pos0 + T > kv.max_len:
+            raise ValueError(f"session {kv.session_id}: {pos0}+{T} tokens exceed max_length {kv.max_len}")
+        if kv.max_len != self.kv_capacity or kv.data.shape[0] != self.n_slots or kv.data.shape[-1] != self.row_elems:
+            raise ValueError(f"session cache {tuple(kv.data.shape)} does not fit this span "
+                             f"({self.n_slots} slots x {self.kv_capacity} rows x {self.row_elems})")
+        W = self.cfg.hidden
+        want = None if logits_at is None else sorted(set(int(i) for i in logits_at))
+        out = None if self.has_head else torch.empty(T, W, dtype=torch.float32, device=self.device)
+        rows = []
+        last_h = None
+        for c0 in range(0, T, self.max_chunk):
+            n = min(self.max_chunk, T - c0)
+            if h_in is None:
+                self.ids_in[:n].copy_(ids[c0:c0 + n], non_blocking=True)
+                x = self._embed(n, pos0 + c0, False)
+            else:
+                x = self.h_a[:n]
+                x.copy_(h_in[c0:c0 + n], non_blocking=True)
+            self._run_layers(n, x, {"kv": kv, "pos0": pos0 + c0})
+            if out is not None:
+                out[c0:c0 + n].copy_(x, non_blocking=True)
+            elif want is not None:
+                sel = [i - c0 for i in want if c0 <= i < c0 + n]
+                if sel:
+                    rows.append(x[torch.tensor(sel, device=self.device)])
+            last_h = x[n - 1:n]
+        kv.length = pos0 + T
+        kv.touch()
+        if not self.has_head:
+            return out
+        if want is None:
+            self.last_hidden = last_h
+            ri = None
+            if greedy == "sample":
+                ri = torch.tensor([getattr(kv, "sampler_row", 0) or 0], dtype=torch.int32, device=self.device)
+            self._head(last_h.clone(), greedy, row_index=ri)
+            return self.logits[:1], self.ids_out[:1]
+        xs = torch.cat(rows, 0) if rows else torch.empty(0, W, dtype=torch.float32, device=self.device)
+        res = torch.empty(len(want), self.cfg.vocab, dtype=torch.float32, device=self.device)
+        res_ids = torch.empty(len(want), dtype=torch.int64, device=self.device)
+        for r0 in range(0, len(want), self.head_rows_max):
+            r1 = min(len(want), r0 + self.head_rows_max)
+            self._head(xs[r0:r1], True)
+            res[r0:r1].copy_(self.logits[:r1 - r0])
+            res_ids[r0:r1].copy_(self.ids_out[:r1 - r0])
+        order = {p: k for k, p in enumerate(want)}
+        pick = torch.tensor([order[int(i)] for i in logits_at], device=self.device)
+        return res[pick], res_ids[pick]
+
+    def forward(self, h: torch.Tensor, kv: SessionKV, pos0: Optional[int] = None) -> torch.Tensor:
+        assert not self.has_head
+        if h.shape[0] == 1 and (pos0 is None or pos0 == kv.length):
+            return self.decode([kv], h_in=h).clone()
+        return self.prefill(kv, h_in=h, pos0=pos0)
+
+
+def make_span(cfg, weights, device, dtype, **kw):
+    """The span class of a configuration's family (the one place the runtime chooses between them)."""
+    if getattr(cfg, "family", "") == "gigezen":
+        return LayeredSpan(cfg, weights, device, dtype, **kw)
+    return NativeSpan(cfg, weights, device, dtype, **kw)
+
+
+def span_runs_natively(cfg, device, dtype) -> bool:
+    """Does the family have a CUDA span for this element type?"""
+    if torch.device(device).type != "cuda":
+        return False
+    if getattr(cfg, "family", "") == "gigezen":
+        return dtype in (torch.float16, torch.bfloat16, torch.float32)
+    return dtype in (torch.float16, torch.bfloat16)

@@ -247,6 +247,11 @@ class NativeSpan:
             v._make_stage_buffers(b - a)       # its graphs read its own positions and cache pointers
         return v
 
+    def _cache_slots(self) -> int:
+        """Rows of the cache pointer table = planes of a session's cache the step addresses (one per block here; a
+        span whose layers share caches has fewer)."""
+        return self.n_layers
+
     def _iter_layers(self):
         """(index, packed weights) of every block in order; a span that streams blocks from the host overrides this."""
         return enumerate(self.layers)
@@ -515,7 +520,7 @@ class NativeSpan:
             if tab is None:
                 # (a served stage batches whatever sessions are queued, so new tuples are the common case there: the
                 # table is assembled from one cached [layers, 2] column per session, not element by element)
-                nl = self.n_layers
+                nl = self._cache_slots()
                 tab = torch.zeros(max(nl, 1), self.max_batch, 2, dtype=torch.int64)
                 for b, kv in enumerate(kvs):
                     if kv.max_len != self.kv_capacity:

@@ -49,7 +49,7 @@ class StageWeights:
 
 def load_stage_weights(model_name: str, device, role: str, *, start: int = 0, end: Optional[int] = None,
                        dtype: torch.dtype = torch.float16, use_cpu_offload: bool = False, seed: int = 0,
-                       families=("llama", "gpt2")) -> StageWeights:
+                       families=("llama", "gpt2", "gigezen")) -> StageWeights:
     cfg = resolve_config(model_name)
     if cfg.family not in families:
         raise ValueError(f"{model_name}: family {cfg.family!r} is not handled by this module ({families})")
@@ -86,7 +86,9 @@ class _StageBase(torch.nn.Module):
         self.keep_layers_on_gpu = keep_layers_on_gpu
         self.use_cpu_offload = full.use_cpu_offload
         self.kv_capacity = kv_capacity
-        native_ok = self.device.type == "cuda" and self.dtype in (torch.float16, torch.bfloat16)
+        from .layered_span import make_span, span_runs_natively
+
+        native_ok = span_runs_natively(self.cfg, self.device, self.dtype)
         self.backend = backend or ("native" if native_ok else "torch")
         if self.backend == "native" and full.use_cpu_offload:
             # weights stay in pinned host memory (packed), two device slots stream them under the sm_100a kernels
@@ -96,10 +98,8 @@ class _StageBase(torch.nn.Module):
                                                    keep_layers_on_gpu=keep_layers_on_gpu, kv_capacity=kv_capacity,
                                                    max_batch=max_batch)
         elif self.backend == "native":
-            from .native_span import NativeSpan
-
-            self.span = NativeSpan(self.cfg, full.weights, self.device, self.dtype, kv_capacity=kv_capacity,
-                                   max_batch=max_batch, weight_format=weight_format)
+            self.span = make_span(self.cfg, full.weights, self.device, self.dtype, kv_capacity=kv_capacity,
+                                  max_batch=max_batch, weight_format=weight_format)
         elif full.use_cpu_offload and self.device.type == "cuda":
             from .offload import OffloadedSpan
 
@@ -110,6 +110,11 @@ class _StageBase(torch.nn.Module):
             if self.device != full.device or full.use_cpu_offload:
                 w = _to_device(w, self.device)
             self.span = TorchSpan(self.cfg, w, self.device, self.dtype)
+
+    @property
+    def hidden_dtype(self) -> torch.dtype:
+        """Element type of the hidden states between stages (fp32 for designs with an fp32 residual stream)."""
+        return getattr(self.span, "hidden_dtype", self.dtype)
 
     def subspan(self, start: int, end: int) -> "_StageBase":
         """Stage object over blocks [start, end) of THIS server's span (absolute block numbers): the same weights, own
@@ -215,8 +220,8 @@ class _StageBase(torch.nn.Module):
 
     # ---- KV helpers (the handler owns the manager; tests may let the stage own one)
     def new_kv_manager(self, **kw) -> KVCacheManager:
-        return KVCacheManager(self.end - self.start, self.cfg.n_kv_heads, self.cfg.head_dim, self.dtype,
-                              self.device, default_max_length=self.kv_capacity, **kw)
+        return KVCacheManager.for_span(self.cfg, self.start, self.end, self.dtype, self.device,
+                                       default_max_length=self.kv_capacity, **kw)
 
     @staticmethod
     def _pos0(position_ids, kv: SessionKV) -> int:
@@ -240,7 +245,7 @@ class _StageBase(torch.nn.Module):
             raise ValueError("decode_batch serves server stages (hidden-state inputs)")
         self.last_greedy_ids = None
         if self.backend == "native" and B <= self.span.max_batch:
-            h = hidden.reshape(B, self.cfg.hidden).to(self.device, self.dtype)
+            h = hidden.reshape(B, self.cfg.hidden).to(self.device, self.hidden_dtype)
             if self.role == "last":
                 logits, ids = self.span.decode(list(kvs), h_in=h, greedy=True)
                 out = logits[:B].clone()
@@ -306,7 +311,7 @@ class StageSegment(_StageBase):
     def forward(self, hidden_states, position_ids=None, attention_mask=None, past_key_values: SessionKV = None,
                 use_cache: bool = True) -> Tuple[torch.Tensor, SessionKV]:
         kv = past_key_values
-        h = hidden_states.reshape(-1, self.cfg.hidden).to(self.device, self.dtype)
+        h = hidden_states.reshape(-1, self.cfg.hidden).to(self.device, self.hidden_dtype)
         h = self._run_blocks(h, kv, self._pos0(position_ids, kv))
         return h.unsqueeze(0), kv
 
@@ -322,7 +327,7 @@ class StageLast(_StageBase):
                 use_cache: bool = True) -> Tuple[torch.Tensor, SessionKV]:
         """-> (logits [1, 1, V] fp32 of the LAST position, kv)."""
         kv = past_key_values
-        h = hidden_states.reshape(-1, self.cfg.hidden).to(self.device, self.dtype)
+        h = hidden_states.reshape(-1, self.cfg.hidden).to(self.device, self.hidden_dtype)
         pos0 = self._pos0(position_ids, kv)
         if pos0 != kv.length:
             kv.rollback(pos0)

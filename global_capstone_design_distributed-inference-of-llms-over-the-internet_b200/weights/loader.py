@@ -57,6 +57,10 @@ def hf_global_names(cfg: ModelConfig) -> Dict[str, str]:
 
 def hf_shapes(cfg: ModelConfig) -> Dict[str, tuple]:
     """Shape of every HF tensor of the architecture (drives random init and tests)."""
+    if cfg.family == "gigezen":
+        from ..models import gigezen
+
+        return gigezen.tensor_shapes(cfg)
     H, I, V = cfg.hidden, cfg.intermediate, cfg.vocab
     out: Dict[str, tuple] = {}
     for i in range(cfg.n_layers):
@@ -146,6 +150,13 @@ class RandomSource:
             g = torch.Generator(device="cpu")
             g.manual_seed(_name_seed(name, self.seed))
             t = torch.randn(shape, generator=g, dtype=torch.float32)
+        if self.cfg.family == "gigezen":
+            # gains stored around zero (layer / final norms), a plain gain for the latent, fan-in scaling elsewhere
+            if name.endswith("dkv.norm"):
+                return 1.0 + 0.1 * t
+            if len(shape) == 1:
+                return 0.1 * t
+            return t * (1.0 if name == "embed" else float(shape[1]) ** -0.5)
         if is_norm_w:
             t = 1.0 + 0.05 * t
         else:
@@ -191,12 +202,46 @@ def load_layer(cfg: ModelConfig, src, i: int, dtype: torch.dtype, device) -> Dic
             "down_w": tr(src.get(n["proj_w"])), "down_b": mv(src.get(n["proj_b"]))}
 
 
+def load_gigezen_layer(cfg, src, i: int, dtype: torch.dtype, device) -> Dict[str, torch.Tensor]:
+    """Canonical tensors of one Gigezen layer: linear weights ``[out, in]`` in ``dtype``, norm gains in fp32, the
+    experts of a mixture stacked (``e_gate`` / ``e_up`` ``[E, ff, W]``, ``e_down`` ``[E, W, ff]``)."""
+    from ..models.gigezen import GatedMLPSpec, MoESpec
+
+    L, p = cfg.layers[i], f"l{i}."
+    mv = lambda n: src.get(p + n).to(device=device, dtype=dtype).contiguous()  # noqa: E731
+    f32 = lambda n: src.get(p + n).to(device=device, dtype=torch.float32).contiguous()  # noqa: E731
+    out = {"norm1_w": f32("norm1"), "q_w": mv("mix.q"), "uk_w": mv("mix.uk"), "uv_w": mv("mix.uv"), "o_w": mv("mix.o")}
+    if L.mixer.owns_cache:
+        out["dkv_w"], out["dkv_norm_w"] = mv("mix.dkv"), f32("mix.dkv.norm")
+    if isinstance(L.mlp, GatedMLPSpec):
+        out.update(gate_w=mv("mlp.gate"), up_w=mv("mlp.up"), down_w=mv("mlp.down"))
+    elif isinstance(L.mlp, MoESpec):
+        out["router_w"] = mv("mlp.router")
+        for k in ("gate", "up", "down"):
+            out["e_" + k] = torch.stack([mv(f"mlp.e{e}.{k}") for e in range(L.mlp.experts)])
+    return out
+
+
+def _load_gigezen_span(cfg, src, start, end, need_embed, need_head, dtype, device) -> Dict[str, object]:
+    cfg.check_span(start, end)
+    out: Dict[str, object] = {"layers": [load_gigezen_layer(cfg, src, i, dtype, device) for i in range(start, end)],
+                              "start": start, "end": end, "has_embed": bool(need_embed), "has_head": bool(need_head)}
+    if need_embed:
+        out["embed"] = src.get("embed").to(device=device, dtype=dtype).contiguous()
+    if need_head:
+        out["final_norm_w"] = src.get("final.norm").to(device=device, dtype=torch.float32).contiguous()
+        out["lm_head"] = src.get("head").to(device=device, dtype=dtype).contiguous()
+    return out
+
+
 def load_span(model: str, cfg: ModelConfig, start: int, end: int, *, need_embed: bool, need_head: bool,
               dtype: torch.dtype, device, seed: int = 0, src=None) -> Dict[str, object]:
     """Weights for decoder blocks [start, end) (+ embedding / final norm + head)."""
     if not (0 <= start <= end <= cfg.n_layers):
         raise ValueError(f"bad span [{start}, {end}) for a {cfg.n_layers}-layer model")
     src = src or open_source(model, cfg, seed, device)
+    if cfg.family == "gigezen":
+        return _load_gigezen_span(cfg, src, start, end, need_embed, need_head, dtype, device)
     out: Dict[str, object] = {"layers": [load_layer(cfg, src, i, dtype, device) for i in range(start, end)],
                               "start": start, "end": end, "has_embed": bool(need_embed),
                               "has_head": bool(need_head)}

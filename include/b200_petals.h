@@ -346,6 +346,112 @@ int32_t b200_sample_state_bytes(void);
 int b200_sample_stateful(const float* logits, int32_t ld, int32_t T, int32_t V, void* rows, void* states,
                          const int32_t* row_index, float* probs, void* out_ids, int32_t pdl, void* stream);
 
+
+/* =====================================================================================================
+ * Mechanisms for layer-list decoder designs with an fp32 residual stream (first user: Gigezen).
+ * Activations that enter a tensor-core GEMM are 16-bit; the residual stream, norms, rotary angles,
+ * attention scores and weights, and routers are fp32.  Element type codes: B200_F16 / B200_BF16 / B200_F32.
+ * The reference has no counterpart (its blocks are HF Llama layers, petals/llama/block.py).
+ * ===================================================================================================== */
+#define B200_F32 2
+
+/* out[t, :] = table[ids[t], :] as fp32 (table 16-bit or fp32); ids int64 on the device. */
+int b200_embed_f32(const void* ids, const void* table, int32_t table_dtype, float* out, int32_t T, int32_t width,
+                   int32_t ldo, int32_t vocab, int32_t pdl, void* stream);
+
+/* Residual update + RMS norm in one pass over the fp32 stream, one block per token:
+ *     x[t] += add_a[t] + add_b[t] + sum_k pair_w[t*top+k] * pair_y[t*top+k]        (each term optional)
+ *     out[t] = x[t] / sqrt(mean(x[t]^2) + eps) * (gain_offset + gain)               (out optional)
+ * gain is fp32; gain_offset = 1 for gains stored around zero, 0 for plain gains.  out: 16-bit or fp32, row stride ldo
+ * (columns beyond width are not touched).  The k-sum runs in index order (bit-reproducible). */
+typedef struct b200_add_norm_args {
+    float* x;
+    const float* add_a;
+    const float* add_b;
+    const float* pair_y;
+    const float* pair_w;
+    const float* gain;
+    void* out;
+    int32_t T, width, ldx, lda, ldb, ldp, top, ldo, out_dtype;
+    float eps, gain_offset;
+    int32_t pdl;
+} b200_add_norm_args;
+int b200_add_rms_norm(const b200_add_norm_args* args, void* stream);
+
+/* Gated unit with clamps: g = min(gate, limit), u = clamp(up, -limit, limit), act = g * sigmoid(alpha * g) * (u + up_shift).
+ * gate/up: fp32 [T, ff] each (row stride ld); act: 16-bit or fp32 [T, ff] (row stride ldo).  limit <= 0: no clamps. */
+int b200_glu_clamp(const float* gate, const float* up, int32_t ld, void* act, int32_t ldo, int32_t out_dtype, int32_t T,
+                   int32_t ff, float limit, float alpha, float up_shift, int32_t pdl, void* stream);
+
+/* Plain fp32-accumulating GEMM on the CUDA cores: out[r, n] = sum_k x[src(r), k] * w[g(r)][n, k].
+ * True 32-bit products (fmaf), used where the tensor-core GEMM's 16-bit operands are not allowed (the all-fp32 mode)
+ * and for the small batched / grouped products around latent attention and the experts of a mixture.
+ *   batch > 1: independent problems b = 0..batch-1 at x + b*x_bs, w + b*w_bs, out + b*o_bs (element strides).
+ *   group_off != NULL: rows [group_off[g], group_off[g+1]) use weight w + g*w_gs (device table, groups + 1 ints);
+ *                      T is then an upper bound of group_off[groups].
+ *   row_src / row_dst: optional gather of x rows / scatter of out rows (ints per problem row).
+ *   w2 != NULL: out = silu(x.w^T) * (x.w2^T)   (gate / up of an expert).
+ *   row_scale: optional factor per problem row, applied last. */
+typedef struct b200_simt_gemm_args {
+    const void* x;
+    const void* w;
+    const void* w2;
+    void* out;
+    const int32_t* row_src;
+    const int32_t* row_dst;
+    const int32_t* group_off;
+    const float* row_scale;
+    int32_t T, N, K, ldx, ldw, ldo;
+    int32_t x_dtype, w_dtype, out_dtype;
+    int32_t batch, groups;
+    int64_t x_bs, w_bs, o_bs, w_gs;
+    int32_t pdl, reserved;
+} b200_simt_gemm_args;
+int b200_gemm_simt(const b200_simt_gemm_args* args, void* stream);
+
+/* Latent attention, step 1: rotary positions and cache append, one block per token.
+ *   proj[t]: fp32 row holding q (heads x [dim unrotated | rot rotated]) at column q_off and, at kv_off (< 0: this
+ *   layer reads another layer's cache and writes nothing), [kv_rank latent | rot shared rotated key].
+ *   q's rotated parts are rotated in place.  The latent is RMS-normed (plain gain, fp32) and stored with the rotated
+ *   key part as one cache row [kv_rank + rot] (16-bit or fp32) at the token's position.
+ *   Rotation: the first rot_dims of the rot part, pairs (i, i + rot_dims/2), angle = pos * inv_freq[i] evaluated in
+ *   double precision (inv_freq: double [rot_dims/2]).
+ *   Cache row of token t: kv_ptrs ? kv_ptrs[t * kv_ptr_stride] + pos[t] * row_bytes : cache + (pos0 + t) * row_bytes. */
+typedef struct b200_latent_args {
+    float* proj;
+    int32_t ldp, q_off, kv_off;
+    const float* c_gain;
+    const double* inv_freq;
+    void* cache;
+    const uint64_t* kv_ptrs;
+    const int32_t* pos;
+    int32_t kv_ptr_stride, pos0;
+    int32_t T, heads, dim, rot, rot_dims, kv_rank, row_elems, cache_dtype;
+    float eps;
+    /* step 2 (b200_latent_attn) */
+    const float* q_abs;   /* [T, heads, kv_rank] fp32: unrotated query pulled through the key up-projection */
+    float* out;           /* [T, heads, kv_rank] fp32: softmax-weighted sum of latents */
+    int32_t ldqa, ldout, window;
+    float scale;
+    int32_t pdl, reserved;
+} b200_latent_args;
+int b200_latent_rope_append(const b200_latent_args* args, void* stream);
+/* Step 2: scores s(j) = (q_abs . c_j + q_rot . kr_j) * scale over the cached rows j with 0 <= pos - j < window,
+ * softmax in fp32, out = sum_j p_j c_j.  All heads of a token share the cached rows (one block = one token x 8 heads,
+ * keys staged through shared memory 32 at a time). */
+int b200_latent_attn(const b200_latent_args* args, void* stream);
+
+/* Router of a mixture of experts, one warp per token: scores = softmax(logits) over all experts (fp32);
+ * experts form `groups` equal groups of neighbours, a group's score is its largest score, only experts of the
+ * `keep` best groups can be chosen; the `top` largest allowed scores win (lowest index on ties).
+ * ids [T, top] int32, weights [T, top] fp32 = the chosen scores (renorm != 0: divided by their sum). */
+int b200_moe_route(const float* logits, int32_t ld, int32_t T, int32_t experts, int32_t groups, int32_t keep, int32_t top,
+                   int32_t renorm, int32_t* ids, float* weights, int32_t pdl, void* stream);
+/* Sorts the T*top (token, slot) pairs by expert (single block): group_off [experts + 1], row_pair [T*top] (pair
+ * index t*top+k per sorted row) and row_token [T*top] (t per sorted row). */
+int b200_moe_plan(const int32_t* ids, int32_t T, int32_t top, int32_t experts, int32_t* group_off, int32_t* row_pair,
+                  int32_t* row_token, int32_t pdl, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
