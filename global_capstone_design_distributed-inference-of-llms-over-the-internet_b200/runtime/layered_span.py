@@ -152,7 +152,7 @@ class LayeredSpan(NativeSpan):
             self.chain_tokens = 0
             self._ptr_tables = {}
             if self.has_head:
-                self.head_rows_max = max(self.max_batch, 32)
+                self.head_rows_max = min(max(self.max_batch, 32), Tm)      # rows per head call (they pass through hn)
                 self.logits = f32(self.head_rows_max, cfg.vocab)
                 self.ids_out = torch.zeros(self.head_rows_max, dtype=torch.int64, device=self.device)
                 self.argmax_ws = E.ArgmaxWorkspace(self.device, self.head_rows_max)
