@@ -53,6 +53,11 @@ def parse_args():
                     help="decode hop between stages: in-graph peer stores (default) or host-issued NCCL send/recv")
     ap.add_argument("--head-split", type=int, default=None, help="1/0: shard the LM head over the last and first stage")
     ap.add_argument("--no-ttft", action="store_true", help="skip the time-to-first-token measurement")
+    ap.add_argument("--designs", action="store_true",
+                    help="instead of the headline run: prefill / decode throughput of the layer-list design (Gigezen) beside "
+                         "Llama at equal layer sizes (scripts/bench_designs.py), one JSON line per size and design")
+    ap.add_argument("--design-sizes", default="small,7b")
+    ap.add_argument("--design-only", default="", help="comma list of designs to run (llama, gigezen)")
     return ap.parse_args()
 
 
@@ -285,7 +290,11 @@ def run_b200(args):
 
 def main():
     args = parse_args()
-    if args.impl == "reference":
+    if args.designs:
+        from scripts.bench_designs import run as run_designs
+
+        run_designs(args)
+    elif args.impl == "reference":
         from baseline.reference_arm import run_reference
 
         run_reference(args)
