@@ -71,8 +71,10 @@ __global__ void __launch_bounds__(128) latent_rope_append_kernel(b200_latent_arg
 constexpr int kHeadsPerBlock = 8;
 constexpr int kChunk = 32;
 
+// splits > 1 (decode sizes): blockIdx.z takes a contiguous share of the window's keys and leaves its unnormalised
+// (acc, m, l) in `part` [T][heads][splits][kv_rank + 2]; latent_merge_kernel combines the shares in index order.
 template <int NPER>
-__global__ void __launch_bounds__(256) latent_attn_kernel(b200_latent_args a) {
+__global__ void __launch_bounds__(256) latent_attn_kernel(b200_latent_args a, int splits, float* __restrict__ part) {
     extern __shared__ float sm[];
     pdl_wait_prior_grid();
     pdl_launch_dependents();
@@ -84,7 +86,13 @@ __global__ void __launch_bounds__(256) latent_attn_kernel(b200_latent_args a) {
     const int h = blockIdx.y * kHeadsPerBlock + warp;
     const bool live = h < a.heads;
     const int p = a.pos ? a.pos[t] : a.pos0 + t;
-    const int lo = p - a.window + 1 > 0 ? p - a.window + 1 : 0;
+    int lo = p - a.window + 1 > 0 ? p - a.window + 1 : 0;
+    int hi = p;                                              // last key of this block's share
+    if (splits > 1) {
+        const int per = ((p - lo + splits) / splits + kChunk - 1) / kChunk * kChunk;
+        lo += blockIdx.z * per;
+        hi = lo + per - 1 < p ? lo + per - 1 : p;
+    }
     if (live) {
         const float* qa = a.q_abs + (size_t)t * a.ldqa + (size_t)h * R;
         const float* qr = a.proj + (size_t)t * a.ldp + a.q_off + h * (a.dim + rot) + a.dim;
@@ -97,8 +105,8 @@ __global__ void __launch_bounds__(256) latent_attn_kernel(b200_latent_args a) {
     float m = -INFINITY, l = 0.f, acc[NPER];
 #pragma unroll
     for (int i = 0; i < NPER; ++i) acc[i] = 0.f;
-    for (int j0 = lo; j0 <= p; j0 += kChunk) {
-        const int n = p - j0 + 1 < kChunk ? p - j0 + 1 : kChunk;
+    for (int j0 = lo; j0 <= hi; j0 += kChunk) {
+        const int n = hi - j0 + 1 < kChunk ? hi - j0 + 1 : kChunk;
         __syncthreads();                                     // previous chunk fully consumed (and qs written)
         for (int e = tid; e < n * E; e += 256) {
             const int j = e / E, d = e - j * E;
@@ -112,9 +120,16 @@ __global__ void __launch_bounds__(256) latent_attn_kernel(b200_latent_args a) {
         if (lane < n) {
             const float* q = qs + warp * E;
             const float* k = kc + lane * ldk;
-            float d0 = 0.f;
-            for (int d = 0; d < E; ++d) d0 = fmaf(q[d], k[d], d0);
-            s = d0 * a.scale;
+            float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;   // four chains: the sum is latency-bound otherwise
+            int d = 0;
+            for (; d + 4 <= E; d += 4) {
+                d0 = fmaf(q[d], k[d], d0);
+                d1 = fmaf(q[d + 1], k[d + 1], d1);
+                d2 = fmaf(q[d + 2], k[d + 2], d2);
+                d3 = fmaf(q[d + 3], k[d + 3], d3);
+            }
+            for (; d < E; ++d) d0 = fmaf(q[d], k[d], d0);
+            s = ((d0 + d1) + (d2 + d3)) * a.scale;
         }
         float cm = s;
 #pragma unroll
@@ -140,6 +155,19 @@ __global__ void __launch_bounds__(256) latent_attn_kernel(b200_latent_args a) {
         }
     }
     if (!live) return;
+    if (splits > 1) {                                        // (a share without keys leaves m = -inf, l = 0)
+        float* o = part + (((size_t)t * a.heads + h) * splits + blockIdx.z) * (R + 2);
+#pragma unroll
+        for (int i = 0; i < NPER; ++i) {
+            const int d = lane + 32 * i;
+            if (d < R) o[d] = acc[i];
+        }
+        if (lane == 0) {
+            o[R] = m;
+            o[R + 1] = l;
+        }
+        return;
+    }
     float* o = a.out + (size_t)t * a.ldout + (size_t)h * R;
     const float inv = 1.0f / l;
 #pragma unroll
@@ -149,12 +177,42 @@ __global__ void __launch_bounds__(256) latent_attn_kernel(b200_latent_args a) {
     }
 }
 
+// One warp per (token, head): the shares' (acc, m, l) merged in index order, then normalised.
+__global__ void __launch_bounds__(128) latent_merge_kernel(const float* __restrict__ part, float* __restrict__ out, int ldout,
+                                                          int T, int heads, int R, int splits) {
+    pdl_wait_prior_grid();
+    pdl_launch_dependents();
+    const int w = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (w >= T * heads) return;
+    const int t = w / heads, h = w - t * heads;
+    const float* p = part + (size_t)w * splits * (R + 2);
+    float m = -INFINITY;
+    for (int s = 0; s < splits; ++s) m = fmaxf(m, p[(size_t)s * (R + 2) + R]);
+    float l = 0.f;
+    for (int s = 0; s < splits; ++s) {
+        const float ms = p[(size_t)s * (R + 2) + R];
+        if (ms > -INFINITY) l += p[(size_t)s * (R + 2) + R + 1] * expf(ms - m);
+    }
+    const float inv = 1.0f / l;
+    for (int d = lane; d < R; d += 32) {
+        float acc = 0.f;
+        for (int s = 0; s < splits; ++s) {
+            const float ms = p[(size_t)s * (R + 2) + R];
+            if (ms > -INFINITY) acc += p[(size_t)s * (R + 2) + d] * expf(ms - m);
+        }
+        out[(size_t)t * ldout + (size_t)h * R + d] = acc * inv;
+    }
+}
+
 template <int NPER>
-static int launch_attn(const b200_latent_args* a, size_t smem, cudaStream_t s) {
+static int launch_attn(const b200_latent_args* a, size_t smem, cudaStream_t s, int splits, float* part) {
     if (smem > 48 * 1024)
         B200_CUDA_CHECK(cudaFuncSetAttribute(latent_attn_kernel<NPER>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    dim3 grid(a->T, (a->heads + kHeadsPerBlock - 1) / kHeadsPerBlock);
-    B200_CUDA_CHECK(launch(latent_attn_kernel<NPER>, grid, dim3(256), smem, s, a->pdl != 0, *a));
+    dim3 grid(a->T, (a->heads + kHeadsPerBlock - 1) / kHeadsPerBlock, splits);
+    B200_CUDA_CHECK(launch(latent_attn_kernel<NPER>, grid, dim3(256), smem, s, a->pdl != 0, *a, splits, part));
+    if (splits > 1)
+        B200_CUDA_CHECK(launch(latent_merge_kernel, dim3((a->T * a->heads + 3) / 4), dim3(128), 0, s, a->pdl != 0,
+                               (const float*)part, a->out, a->ldout, a->T, a->heads, a->kv_rank, splits));
     return B200_OK;
 }
 
@@ -182,19 +240,28 @@ extern "C" int b200_latent_rope_append(const b200_latent_args* a, void* stream) 
     return B200_OK;
 }
 
+extern "C" int64_t b200_latent_attn_scratch_bytes(int32_t T, int32_t heads, int32_t kv_rank, int32_t splits) {
+    return (int64_t)T * heads * splits * (kv_rank + 2) * (int64_t)sizeof(float);
+}
+
 extern "C" int b200_latent_attn(const b200_latent_args* a, void* stream) {
+    return b200_latent_attn_split(a, 1, nullptr, stream);
+}
+
+extern "C" int b200_latent_attn_split(const b200_latent_args* a, int32_t splits, float* scratch, void* stream) {
     if (int rc = check_latent(a, "b200_latent_attn")) return rc;
+    if (splits < 1 || splits > 64 || (splits > 1 && !scratch)) return fail(B200_EINVAL, "b200_latent_attn: bad splits %d", splits);
     if (!a->q_abs || !a->out || a->window <= 0) return fail(B200_EINVAL, "b200_latent_attn: q_abs / out / window missing");
     const int E = a->kv_rank + a->rot;
     const size_t smem = ((size_t)kHeadsPerBlock * E + (size_t)kChunk * (E | 1)) * sizeof(float);
     if (smem > 220 * 1024) return fail(B200_ELIMIT, "b200_latent_attn: kv_rank + rot = %d exceeds shared memory", E);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const int nper = (a->kv_rank + 31) / 32;
-    if (nper <= 1) return launch_attn<1>(a, smem, s);
-    if (nper <= 2) return launch_attn<2>(a, smem, s);
-    if (nper <= 4) return launch_attn<4>(a, smem, s);
-    if (nper <= 8) return launch_attn<8>(a, smem, s);
-    if (nper <= 16) return launch_attn<16>(a, smem, s);
-    if (nper <= 32) return launch_attn<32>(a, smem, s);
+    if (nper <= 1) return launch_attn<1>(a, smem, s, splits, scratch);
+    if (nper <= 2) return launch_attn<2>(a, smem, s, splits, scratch);
+    if (nper <= 4) return launch_attn<4>(a, smem, s, splits, scratch);
+    if (nper <= 8) return launch_attn<8>(a, smem, s, splits, scratch);
+    if (nper <= 16) return launch_attn<16>(a, smem, s, splits, scratch);
+    if (nper <= 32) return launch_attn<32>(a, smem, s, splits, scratch);
     return fail(B200_ELIMIT, "b200_latent_attn: kv_rank %d > 1024", a->kv_rank);
 }

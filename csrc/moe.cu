@@ -126,9 +126,39 @@ __global__ void __launch_bounds__(1024) moe_plan_kernel(const int* __restrict__ 
     }
 }
 
+// act[t, e * ff + j] *= weight of expert e for token t (0 when e was not chosen): turns the outputs of ALL experts'
+// gated units into the operand of one down-projection over the concatenated experts.
+__global__ void __launch_bounds__(256) moe_scale_kernel(uint16_t* __restrict__ act, int ld, const int* __restrict__ ids,
+                                                       const float* __restrict__ wts, int T, int E, int ff, int top, int is_bf16) {
+    pdl_wait_prior_grid();
+    pdl_launch_dependents();
+    const int t = blockIdx.y;
+    const int n = E * ff;
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
+        const int e = i / ff;
+        float w = 0.f;
+        for (int k = 0; k < top; ++k)
+            if (ids[(size_t)t * top + k] == e) w += wts[(size_t)t * top + k];
+        uint16_t* p = act + (size_t)t * ld + i;
+        *p = w == 0.f ? (uint16_t)0 : float_to_h16(h16_to_float(*p, is_bf16) * w, is_bf16);
+    }
+}
+
 }  // namespace b200
 
 using namespace b200;
+
+extern "C" int b200_moe_scale(void* act, int32_t ld, int32_t dtype, const int32_t* ids, const float* weights, int32_t T,
+                              int32_t experts, int32_t ff, int32_t top, int32_t pdl, void* stream) {
+    if (!act || !ids || !weights || T <= 0 || experts <= 0 || ff <= 0 || top <= 0 || (dtype != B200_F16 && dtype != B200_BF16))
+        return fail(B200_EINVAL, "b200_moe_scale: bad argument");
+    const int n = experts * ff;
+    dim3 grid((n + 1023) / 1024 < 64 ? (n + 1023) / 1024 : 64, T);
+    if (T > 65535) return fail(B200_ELIMIT, "b200_moe_scale: T %d", T);
+    B200_CUDA_CHECK(launch(moe_scale_kernel, grid, dim3(256), 0, static_cast<cudaStream_t>(stream), pdl != 0,
+                           static_cast<uint16_t*>(act), ld, ids, weights, T, experts, ff, top, dtype == B200_BF16 ? 1 : 0));
+    return B200_OK;
+}
 
 extern "C" int b200_moe_route(const float* logits, int32_t ld, int32_t T, int32_t experts, int32_t groups, int32_t keep,
                               int32_t top, int32_t renorm, int32_t* ids, float* weights, int32_t pdl, void* stream) {

@@ -72,8 +72,11 @@ PROTOTYPES = [
     ("b200_gemm_simt", [C.POINTER(SimtGemmArgs), vp], C.c_int),
     ("b200_latent_rope_append", [C.POINTER(LatentArgs), vp], C.c_int),
     ("b200_latent_attn", [C.POINTER(LatentArgs), vp], C.c_int),
+    ("b200_latent_attn_split", [C.POINTER(LatentArgs), i32, vp, vp], C.c_int),
+    ("b200_latent_attn_scratch_bytes", [i32, i32, i32, i32], i64),
     ("b200_moe_route", [vp, i32, i32, i32, i32, i32, i32, i32, vp, vp, i32, vp], C.c_int),
     ("b200_moe_plan", [vp, i32, i32, i32, vp, vp, vp, i32, vp], C.c_int),
+    ("b200_moe_scale", [vp, i32, i32, vp, vp, i32, i32, i32, i32, i32, vp], C.c_int),
     ("b200_hop_ring_bytes", [i32, i32, i32], i64),
     ("b200_hop_send", [C.POINTER(HopArgs), vp], C.c_int),
     ("b200_hop_recv", [C.POINTER(HopArgs), vp], C.c_int),

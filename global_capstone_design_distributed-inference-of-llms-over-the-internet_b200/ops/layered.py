@@ -117,8 +117,15 @@ def latent_rope_append(a: LatentArgs) -> None:
     native.check(native.lib().b200_latent_rope_append(ctypes.byref(a), _s()), "b200_latent_rope_append")
 
 
-def latent_attn(a: LatentArgs) -> None:
-    native.check(native.lib().b200_latent_attn(ctypes.byref(a), _s()), "b200_latent_attn")
+def latent_attn(a: LatentArgs, splits: int = 1, scratch: Optional[torch.Tensor] = None) -> None:
+    """splits > 1: the keys of every token's window are divided over that many blocks (``scratch``: fp32 tensor of
+    at least T * heads * splits * (kv_rank + 2) elements)."""
+    if splits > 1:
+        assert scratch is not None and scratch.dtype == torch.float32 and \
+            scratch.numel() >= a.T * a.heads * splits * (a.kv_rank + 2)
+        native.check(native.lib().b200_latent_attn_split(ctypes.byref(a), splits, scratch.data_ptr(), _s()), "b200_latent_attn")
+    else:
+        native.check(native.lib().b200_latent_attn(ctypes.byref(a), _s()), "b200_latent_attn")
 
 
 def moe_route(logits: torch.Tensor, experts: int, groups: int, keep: int, top: int, ids: torch.Tensor, weights: torch.Tensor,
@@ -134,3 +141,10 @@ def moe_plan(ids: torch.Tensor, T: int, top: int, experts: int, group_off: torch
              row_token: torch.Tensor, pdl: bool = False) -> None:
     native.check(native.lib().b200_moe_plan(ids.data_ptr(), T, top, experts, group_off.data_ptr(), row_pair.data_ptr(),
                                            row_token.data_ptr(), 1 if pdl else 0, _s()), "b200_moe_plan")
+
+
+def moe_scale(act: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, experts: int, ff: int, top: int,
+              pdl: bool = False) -> None:
+    """act: 16-bit [T, >= experts * ff], scaled in place by each token's routing weights (0 for experts not chosen)."""
+    native.check(native.lib().b200_moe_scale(act.data_ptr(), act.stride(0), code(act.dtype), ids.data_ptr(), weights.data_ptr(),
+                                            act.shape[0], experts, ff, top, 1 if pdl else 0, _s()), "b200_moe_scale")

@@ -33,6 +33,13 @@ from .kv_cache import SessionKV
 from .native_span import MAX_DECODE_BATCH, NativeSpan, _pdl_default
 
 
+# Mixtures whose experts / top ratio is at most this run their experts densely on the tensor cores (16-bit modes).
+DENSE_EXPERTS_MAX_RATIO = int(os.environ.get("B200_DENSE_EXPERTS_MAX_RATIO", "16"))
+
+
+ATTN_MAX_SPLITS = 16
+
+
 def _pad64(n: int) -> int:
     return (n + 63) // 64 * 64
 
@@ -94,7 +101,16 @@ class LayeredSpan(NativeSpan):
                     P["r_off"] = n
                     parts.append(Lw["router_w"])
                     n += S.mlp.experts
-                    P["e_gate"], P["e_up"], P["e_down"] = Lw["e_gate"], Lw["e_up"], Lw["e_down"]
+                    e = S.mlp
+                    if not ex and e.experts <= DENSE_EXPERTS_MAX_RATIO * e.top:
+                        # tensor-core form: ALL experts as one gate/up GEMM (fused gated unit) and one down GEMM over the
+                        # concatenated experts, the routing weights (0 = not chosen) applied in between.  experts / top
+                        # times the FLOPs of the chosen experts alone, on a GEMM that is ~30 times faster than the grouped
+                        # CUDA-core one; a decode step streams every expert once, which a batch of a few tokens does anyway.
+                        P["e_in"] = packing.pack_dual(Lw["e_gate"].reshape(e.experts * e.ff, W), Lw["e_up"].reshape(e.experts * e.ff, W))
+                        P["e_out"] = _Linear(Lw["e_down"].permute(1, 0, 2).reshape(W, e.experts * e.ff), ex)
+                    else:
+                        P["e_gate"], P["e_up"], P["e_down"] = Lw["e_gate"], Lw["e_up"], Lw["e_down"]
                 elif isinstance(S.mlp, Z.GatedMLPSpec):
                     P["g_off"], P["u_off"] = n, n + S.mlp.ff
                     parts += [Lw["gate_w"], Lw["up_w"]]
@@ -113,7 +129,8 @@ class LayeredSpan(NativeSpan):
                 P["hv"] = hv
                 self.layers.append(P)
                 if free_source_weights:
-                    for k in ("q_w", "dkv_w", "router_w", "gate_w", "up_w", "o_w", "down_w", "uk_w"):
+                    for k in ("q_w", "dkv_w", "router_w", "gate_w", "up_w", "o_w", "down_w", "uk_w") + \
+                            (("e_gate", "e_up", "e_down") if "e_in" in P else ()):
                         Lw.pop(k, None)
             self.embed_w = weights.get("embed") if self.has_embed else None
             self.pos_embed_w = None
@@ -134,6 +151,8 @@ class LayeredSpan(NativeSpan):
             self.ol = torch.zeros_like(self.qa)
             self.cat = act(Tm, mx(lambda P: _pad64(P["out"].k)))
             self.y = f32(Tm, W)
+            self.attn_part = f32(MAX_DECODE_BATCH * ATTN_MAX_SPLITS *
+                                 mx(lambda P: P["spec"].mixer.heads * (P["spec"].mixer.kv_rank + 2)))
             moe = [P["spec"].mlp for P in self.layers if isinstance(P["spec"].mlp, Z.MoESpec)]
             if moe:
                 top, ne, ffe = max(e.top for e in moe), max(e.experts for e in moe), max(e.ff for e in moe)
@@ -142,8 +161,10 @@ class LayeredSpan(NativeSpan):
                 self.moe_off = torch.zeros(ne + 1, dtype=torch.int32, device=self.device)
                 self.moe_row_pair = torch.zeros(Tm * top, dtype=torch.int32, device=self.device)
                 self.moe_row_token = torch.zeros(Tm * top, dtype=torch.int32, device=self.device)
-                self.moe_act = f32(Tm * top, ffe)
-                self.moe_y = f32(Tm * top, W)
+                self.moe_act = f32(Tm * top, ffe) if any("e_gate" in P for P in self.layers) else None
+                self.moe_y = f32(Tm * top, W) if self.moe_act is not None else f32(Tm, W)
+                wide = [P["e_out"].k_padded for P in self.layers if "e_out" in P]
+                self.moe_act_all = act(Tm, max(wide)) if wide else None
             self.ids_in = torch.zeros(Tm, dtype=torch.int64, device=self.device)
             self.ws = None if ex else G.GemmWorkspace.create(self.device, Tm)
             self._make_stage_buffers(self.n_slots)
@@ -177,6 +198,8 @@ class LayeredSpan(NativeSpan):
             n += P["proj"].nbytes + P["out"].nbytes + sum(P[k].numel() * P[k].element_size() for k in ("ukT", "uv"))
             if "e_gate" in P:
                 n += sum(P[k].numel() * P[k].element_size() for k in ("e_gate", "e_up", "e_down"))
+            if "e_in" in P:
+                n += P["e_in"].nbytes + P["e_out"].nbytes
         if self.has_head:
             n += self.lm_head.nbytes
         return n
@@ -206,6 +229,16 @@ class LayeredSpan(NativeSpan):
         L.add_rms_norm(x, gain, out, self.cfg.norm_eps, Z.NORM_GAIN_OFFSET, pdl=self.pdl, **pend)
         self._count()
 
+    def _attn_splits(self, T: int, m) -> tuple:
+        """Decode-size steps divide every token's window over several blocks (tokens x head groups alone leave most SMs
+        idle); the split depends on the window and the step's size only, so a captured step keeps it."""
+        if T > MAX_DECODE_BATCH:
+            return 1, None
+        keys = min(m.window, self.kv_capacity)
+        blocks = T * ((m.heads + 7) // 8)
+        splits = max(1, min(ATTN_MAX_SPLITS, keys // 64, (4 * 148) // blocks))
+        return (splits, self.attn_part) if splits > 1 else (1, None)
+
     def _layer(self, T: int, x: torch.Tensor, P: dict, where: dict) -> None:
         S, pdl = P["spec"], self.pdl
         m = S.mixer
@@ -226,7 +259,7 @@ class LayeredSpan(NativeSpan):
         hd = m.dim + m.rot_dim
         L.gemm_simt(proj[:, P["q_off"]:], P["ukT"], self.qa, T=T, N=m.kv_rank, K=m.dim, ldx=proj.stride(0), ldw=m.dim,
                     ldo=m.heads * m.kv_rank, batch=m.heads, x_bs=hd, w_bs=m.kv_rank * m.dim, o_bs=m.kv_rank, pdl=pdl)
-        L.latent_attn(a)
+        L.latent_attn(a, *self._attn_splits(T, m))
         L.gemm_simt(self.ol, P["uv"], cat, T=T, N=m.vdim, K=m.kv_rank, ldx=m.heads * m.kv_rank, ldw=m.kv_rank,
                     ldo=cat.stride(0), batch=m.heads, x_bs=m.kv_rank, w_bs=m.vdim * m.kv_rank, o_bs=m.vdim, pdl=pdl)
         self._count(4)
@@ -244,6 +277,14 @@ class LayeredSpan(NativeSpan):
             if e.top != self.moe_ids.shape[1]:
                 ids, wts = self.moe_ids.view(-1)[:n].view(T, e.top), self.moe_w.view(-1)[:n].view(T, e.top)
             L.moe_route(proj[:, P["r_off"]:P["r_off"] + e.experts], e.experts, e.groups, e.keep, e.top, ids, wts, pdl=pdl)
+            if "e_in" in P:
+                act_all = self.moe_act_all[:T]
+                G.linear(hn, P["e_in"], out=act_all[:, :e.experts * e.ff], epilogue=G.EPI_SWIGLU, workspace=self.ws, pdl=pdl)
+                L.moe_scale(act_all, ids, wts, e.experts, e.ff, e.top, pdl=pdl)
+                self._linear(act_all, P["e_out"], self.moe_y[:T])
+                self._pending["add_b"] = self.moe_y[:T]
+                self._count(3)
+                return
             L.moe_plan(ids, T, e.top, e.experts, self.moe_off, self.moe_row_pair, self.moe_row_token, pdl=pdl)
             grouped = dict(group_off=self.moe_off, groups=e.experts, T=n, pdl=pdl)
             L.gemm_simt(hn, P["e_gate"], self.moe_act, w2=P["e_up"], N=e.ff, K=W, ldw=W, w_gs=e.ff * W,

@@ -440,6 +440,11 @@ int b200_latent_rope_append(const b200_latent_args* args, void* stream);
  * softmax in fp32, out = sum_j p_j c_j.  All heads of a token share the cached rows (one block = one token x 8 heads,
  * keys staged through shared memory 32 at a time). */
 int b200_latent_attn(const b200_latent_args* args, void* stream);
+/* The same with the window's keys of every token divided over `splits` blocks (decode sizes, where tokens x heads alone
+ * do not fill the GPU); the shares meet in `scratch` (b200_latent_attn_scratch_bytes) and are merged in index order by a
+ * second launch.  splits = 1 is b200_latent_attn. */
+int b200_latent_attn_split(const b200_latent_args* args, int32_t splits, float* scratch, void* stream);
+int64_t b200_latent_attn_scratch_bytes(int32_t T, int32_t heads, int32_t kv_rank, int32_t splits);
 
 /* Router of a mixture of experts, one warp per token: scores = softmax(logits) over all experts (fp32);
  * experts form `groups` equal groups of neighbours, a group's score is its largest score, only experts of the
@@ -449,6 +454,11 @@ int b200_moe_route(const float* logits, int32_t ld, int32_t T, int32_t experts, 
                    int32_t renorm, int32_t* ids, float* weights, int32_t pdl, void* stream);
 /* Sorts the T*top (token, slot) pairs by expert (single block): group_off [experts + 1], row_pair [T*top] (pair
  * index t*top+k per sorted row) and row_token [T*top] (t per sorted row). */
+/* Dense form of the experts for tensor-core GEMMs: after ONE gate/up GEMM over all experts' concatenated rows
+ * (act [T, experts * ff], 16-bit), every token's slice of expert e is multiplied by that expert's routing weight
+ * (0 when it was not chosen), so that ONE down GEMM over the concatenated experts yields the weighted sum. */
+int b200_moe_scale(void* act, int32_t ld, int32_t dtype, const int32_t* ids, const float* weights, int32_t T,
+                   int32_t experts, int32_t ff, int32_t top, int32_t pdl, void* stream);
 int b200_moe_plan(const int32_t* ids, int32_t T, int32_t top, int32_t experts, int32_t* group_off, int32_t* row_pair,
                   int32_t* row_token, int32_t pdl, void* stream);
 

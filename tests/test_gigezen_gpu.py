@@ -254,7 +254,7 @@ def _attention_direct(qa, qr, c, kr, p, window, scale):
 
 
 @pytest.mark.parametrize("cache_dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("batched", [False, True])
+@pytest.mark.parametrize("batched", [0, 1, 3, 16], ids=["portion", "table", "table-3-shares", "table-16-shares"])
 def test_latent_attention_window_edges_and_far_keys(cache_dtype, batched):
     """One key per query is made to dominate (a large score) once just inside and once just outside the window, and
     once far back; rows are addressed through the session's cache (a prompt's portion) or through the staged pointer
@@ -290,9 +290,13 @@ def test_latent_attention_window_edges_and_far_keys(cache_dtype, batched):
     inv = torch.ones(rot // 2, dtype=torch.float64, device=DEV)
     if batched:
         ptrs = torch.tensor([[cache[t % 2].data_ptr(), 0] for t in range(T)], dtype=torch.int64, device=DEV)
-        a = L.latent_args(proj, 0, -1, None, inv, T=T, kv_ptrs=ptrs, kv_ptr_stride=2,
-                          pos=torch.tensor(qpos, dtype=torch.int32, device=DEV), **common)
-        L.latent_attn(a)
+        pos_t = torch.tensor(qpos, dtype=torch.int32, device=DEV)       # (the argument struct holds raw pointers: keep
+        scratch = torch.zeros(T * H * max(batched, 1) * (R + 2), device=DEV)   #  every tensor alive until the result is read)
+        a = L.latent_args(proj, 0, -1, None, inv, T=T, kv_ptrs=ptrs, kv_ptr_stride=2, pos=pos_t, **common)
+        if batched > 1:      # the window's keys divided over several blocks (more shares than some windows have chunks)
+            L.latent_attn(a, batched, scratch)
+        else:
+            L.latent_attn(a)
         got = out.cpu().double().view(T, H, R)
     else:
         got = torch.zeros(T, H, R, dtype=torch.float64)
