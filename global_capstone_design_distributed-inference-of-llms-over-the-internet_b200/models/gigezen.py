@@ -95,7 +95,7 @@ class GigezenConfig:
 
     def cache_row(self, start: int = 0, end: Optional[int] = None) -> int:
         rows = [self.layers[i].mixer.row for i in self.cache_layers(start, end)]
-        return (max(rows) + 7) // 8 * 8 if rows else 8
+        return (max(rows) + 63) // 64 * 64 if rows else 64      # (whole 64-element k-blocks: rows are a GEMM operand)
 
     def check_span(self, start: int, end: int) -> None:
         for i in range(start, end):

@@ -74,6 +74,8 @@ PROTOTYPES = [
     ("b200_latent_attn", [C.POINTER(LatentArgs), vp], C.c_int),
     ("b200_latent_attn_split", [C.POINTER(LatentArgs), i32, vp, vp], C.c_int),
     ("b200_latent_attn_scratch_bytes", [i32, i32, i32, i32], i64),
+    ("b200_latent_attn_prefill", [vp, i32, i32, vp, i32, i32, vp, i32, i32, vp, i32, i32, i32, i32, i32, i32, i32, i32, i32,
+                                  f32, i32, i32, vp], C.c_int),
     ("b200_moe_route", [vp, i32, i32, i32, i32, i32, i32, i32, vp, vp, i32, vp], C.c_int),
     ("b200_moe_plan", [vp, i32, i32, i32, vp, vp, vp, i32, vp], C.c_int),
     ("b200_moe_scale", [vp, i32, i32, vp, vp, i32, i32, i32, i32, i32, vp], C.c_int),

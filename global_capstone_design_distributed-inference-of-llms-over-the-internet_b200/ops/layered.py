@@ -148,3 +148,14 @@ def moe_scale(act: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, exper
     """act: 16-bit [T, >= experts * ff], scaled in place by each token's routing weights (0 for experts not chosen)."""
     native.check(native.lib().b200_moe_scale(act.data_ptr(), act.stride(0), code(act.dtype), ids.data_ptr(), weights.data_ptr(),
                                             act.shape[0], experts, ff, top, 1 if pdl else 0, _s()), "b200_moe_scale")
+
+
+def latent_attn_prefill(proj: torch.Tensor, q_off: int, kvx: torch.Tensor, v_off: int, cache: torch.Tensor, kv_rank: int,
+                        out: torch.Tensor, *, T: int, heads: int, dim: int, rot: int, vdim: int, pos0: int, s0: int,
+                        window: int, scale: float, pdl: bool = False) -> None:
+    """Tensor-core attention of a chunk of one session over expanded keys / values (``b200_latent_attn_prefill``)."""
+    assert proj.dtype == torch.float32 and kvx.dtype == cache.dtype == out.dtype and kvx.dtype in (torch.float16, torch.bfloat16)
+    native.check(native.lib().b200_latent_attn_prefill(
+        proj.data_ptr(), proj.stride(0), q_off, kvx.data_ptr(), kvx.stride(0), v_off, cache.data_ptr(), cache.stride(0),
+        kv_rank, out.data_ptr(), out.stride(0), T, heads, dim, rot, vdim, pos0, s0, window, scale, code(out.dtype),
+        1 if pdl else 0, _s()), "b200_latent_attn_prefill")

@@ -38,6 +38,8 @@ DENSE_EXPERTS_MAX_RATIO = int(os.environ.get("B200_DENSE_EXPERTS_MAX_RATIO", "16
 
 
 ATTN_MAX_SPLITS = 16
+# Chunks of one session with at least this many tokens run their attention on the tensor cores (16-bit modes).
+TC_ATTN_MIN_TOKENS = int(os.environ.get("B200_LATENT_TC_MIN_TOKENS", "33"))
 
 
 def _pad64(n: int) -> int:
@@ -119,6 +121,8 @@ class LayeredSpan(NativeSpan):
                 hv = m.heads * m.vdim
                 dense = isinstance(S.mlp, Z.GatedMLPSpec)
                 P["out"] = _Linear(torch.cat([Lw["o_w"], Lw["down_w"]], 1) if dense else Lw["o_w"], ex)
+                if not ex:      # prompt-size chunks expand the visible latents into per-head keys and values with one GEMM
+                    P["kvx_w"] = _Linear(torch.cat([Lw["uk_w"], Lw["uv_w"]], 0), ex)
                 P["ukT"] = Lw["uk_w"].view(m.heads, m.dim, m.kv_rank).transpose(1, 2).contiguous()     # [H, R, dim]
                 P["uv"] = Lw["uv_w"].view(m.heads, m.vdim, m.kv_rank).contiguous()                     # [H, vdim, R]
                 key = (m.rope_base, m.rope_dims)
@@ -166,7 +170,10 @@ class LayeredSpan(NativeSpan):
                 wide = [P["e_out"].k_padded for P in self.layers if "e_out" in P]
                 self.moe_act_all = act(Tm, max(wide)) if wide else None
             self.ids_in = torch.zeros(Tm, dtype=torch.int64, device=self.device)
-            self.ws = None if ex else G.GemmWorkspace.create(self.device, Tm)
+            # expanded keys / values of the rows a chunk can see (16-bit modes, allocated with the first such chunk)
+            self.kvx = None
+            self.kvx_rows = Tm + min(mx(lambda P: P["spec"].mixer.window - 1), self.kv_capacity)
+            self.ws = None if ex else G.GemmWorkspace.create(self.device, max(Tm, min(self.kvx_rows, 256)))
             self._make_stage_buffers(self.n_slots)
             self.sampler = None
             self._seq_host = 0
@@ -256,13 +263,11 @@ class LayeredSpan(NativeSpan):
                           window=m.window, scale=m.scale, **common)
         a.ldqa = a.ldout = m.heads * m.kv_rank
         L.latent_rope_append(a)
-        hd = m.dim + m.rot_dim
-        L.gemm_simt(proj[:, P["q_off"]:], P["ukT"], self.qa, T=T, N=m.kv_rank, K=m.dim, ldx=proj.stride(0), ldw=m.dim,
-                    ldo=m.heads * m.kv_rank, batch=m.heads, x_bs=hd, w_bs=m.kv_rank * m.dim, o_bs=m.kv_rank, pdl=pdl)
-        L.latent_attn(a, *self._attn_splits(T, m))
-        L.gemm_simt(self.ol, P["uv"], cat, T=T, N=m.vdim, K=m.kv_rank, ldx=m.heads * m.kv_rank, ldw=m.kv_rank,
-                    ldo=cat.stride(0), batch=m.heads, x_bs=m.kv_rank, w_bs=m.vdim * m.kv_rank, o_bs=m.vdim, pdl=pdl)
-        self._count(4)
+        self._count()
+        if "kv" in where and not self.exact and T >= TC_ATTN_MIN_TOKENS:
+            self._attn_tensor_core(T, P, where, proj, cat)
+        else:
+            self._attn_latent(T, P, a, proj, cat)
         if isinstance(S.mlp, Z.GatedMLPSpec):
             ff = S.mlp.ff
             L.glu_clamp(proj[:, P["g_off"]:P["g_off"] + ff], proj[:, P["u_off"]:P["u_off"] + ff], cat[:, P["hv"]:],
@@ -271,28 +276,62 @@ class LayeredSpan(NativeSpan):
         self._linear(cat, P["out"], self.y[:T])
         self._pending = dict(add_a=self.y[:T])
         if isinstance(S.mlp, Z.MoESpec):
-            e = S.mlp
-            n = T * e.top
-            ids, wts = self.moe_ids[:T, :e.top], self.moe_w[:T, :e.top]
-            if e.top != self.moe_ids.shape[1]:
-                ids, wts = self.moe_ids.view(-1)[:n].view(T, e.top), self.moe_w.view(-1)[:n].view(T, e.top)
-            L.moe_route(proj[:, P["r_off"]:P["r_off"] + e.experts], e.experts, e.groups, e.keep, e.top, ids, wts, pdl=pdl)
-            if "e_in" in P:
-                act_all = self.moe_act_all[:T]
-                G.linear(hn, P["e_in"], out=act_all[:, :e.experts * e.ff], epilogue=G.EPI_SWIGLU, workspace=self.ws, pdl=pdl)
-                L.moe_scale(act_all, ids, wts, e.experts, e.ff, e.top, pdl=pdl)
-                self._linear(act_all, P["e_out"], self.moe_y[:T])
-                self._pending["add_b"] = self.moe_y[:T]
-                self._count(3)
-                return
-            L.moe_plan(ids, T, e.top, e.experts, self.moe_off, self.moe_row_pair, self.moe_row_token, pdl=pdl)
-            grouped = dict(group_off=self.moe_off, groups=e.experts, T=n, pdl=pdl)
-            L.gemm_simt(hn, P["e_gate"], self.moe_act, w2=P["e_up"], N=e.ff, K=W, ldw=W, w_gs=e.ff * W,
-                        row_src=self.moe_row_token, **grouped)
-            L.gemm_simt(self.moe_act, P["e_down"], self.moe_y, N=W, K=e.ff, ldw=e.ff, w_gs=W * e.ff,
-                        row_dst=self.moe_row_pair, **grouped)
-            self._pending.update(pair_y=self.moe_y, pair_w=wts, top=e.top)
-            self._count(4)
+            self._experts(T, P, hn, proj)
+
+    def _attn_tensor_core(self, T: int, P: dict, where: dict, proj: torch.Tensor, cat: torch.Tensor) -> None:
+        """A chunk of one session: expand the visible latents with one tensor-core GEMM, then flash attention on them."""
+        m = P["spec"].mixer
+        kv, pos0 = where["kv"], where["pos0"]
+        s0 = max(0, pos0 - m.window + 1)
+        rows = pos0 + T - s0
+        w = P["kvx_w"]
+        if self.kvx is None:
+            width = max(Q["kvx_w"].n for Q in self.layers)
+            self.kvx = torch.zeros(self.kvx_rows, (width + 7) // 8 * 8, dtype=self.dtype, device=self.device)
+        cache = kv.rows(P["slot"])
+        G.linear(cache[s0:s0 + rows, :w.k_padded], w.packed, out=self.kvx[:rows, :w.n], workspace=self.ws, pdl=self.pdl)
+        L.latent_attn_prefill(proj, P["q_off"], self.kvx, m.heads * m.dim, cache, m.kv_rank, cat, T=T, heads=m.heads,
+                              dim=m.dim, rot=m.rot_dim, vdim=m.vdim, pos0=pos0, s0=s0, window=m.window, scale=m.scale,
+                              pdl=self.pdl)
+        self._count(2)
+
+    def _attn_latent(self, T: int, P: dict, a, proj: torch.Tensor, cat: torch.Tensor) -> None:
+        """Decode steps and the all-fp32 mode: queries pulled through W_uk, attention over the latents, W_uv after it."""
+        m, pdl = P["spec"].mixer, self.pdl
+        hd = m.dim + m.rot_dim
+        L.gemm_simt(proj[:, P["q_off"]:], P["ukT"], self.qa, T=T, N=m.kv_rank, K=m.dim, ldx=proj.stride(0), ldw=m.dim,
+                    ldo=m.heads * m.kv_rank, batch=m.heads, x_bs=hd, w_bs=m.kv_rank * m.dim, o_bs=m.kv_rank, pdl=pdl)
+        L.latent_attn(a, *self._attn_splits(T, m))
+        L.gemm_simt(self.ol, P["uv"], cat, T=T, N=m.vdim, K=m.kv_rank, ldx=m.heads * m.kv_rank, ldw=m.kv_rank,
+                    ldo=cat.stride(0), batch=m.heads, x_bs=m.kv_rank, w_bs=m.vdim * m.kv_rank, o_bs=m.vdim, pdl=pdl)
+        self._count(3)
+
+    def _experts(self, T: int, P: dict, hn: torch.Tensor, proj: torch.Tensor) -> None:
+        """Mixture of experts of a layer: route, then the experts densely on the tensor cores or grouped on the CUDA
+        cores; leaves its output pending for the next residual update."""
+        pdl, W = self.pdl, self.cfg.hidden
+        e = P["spec"].mlp
+        n = T * e.top
+        ids, wts = self.moe_ids[:T, :e.top], self.moe_w[:T, :e.top]
+        if e.top != self.moe_ids.shape[1]:
+            ids, wts = self.moe_ids.view(-1)[:n].view(T, e.top), self.moe_w.view(-1)[:n].view(T, e.top)
+        L.moe_route(proj[:, P["r_off"]:P["r_off"] + e.experts], e.experts, e.groups, e.keep, e.top, ids, wts, pdl=pdl)
+        if "e_in" in P:
+            act_all = self.moe_act_all[:T]
+            G.linear(hn, P["e_in"], out=act_all[:, :e.experts * e.ff], epilogue=G.EPI_SWIGLU, workspace=self.ws, pdl=pdl)
+            L.moe_scale(act_all, ids, wts, e.experts, e.ff, e.top, pdl=pdl)
+            self._linear(act_all, P["e_out"], self.moe_y[:T])
+            self._pending["add_b"] = self.moe_y[:T]
+            self._count(3)
+            return
+        L.moe_plan(ids, T, e.top, e.experts, self.moe_off, self.moe_row_pair, self.moe_row_token, pdl=pdl)
+        grouped = dict(group_off=self.moe_off, groups=e.experts, T=n, pdl=pdl)
+        L.gemm_simt(hn, P["e_gate"], self.moe_act, w2=P["e_up"], N=e.ff, K=W, ldw=W, w_gs=e.ff * W,
+                    row_src=self.moe_row_token, **grouped)
+        L.gemm_simt(self.moe_act, P["e_down"], self.moe_y, N=W, K=e.ff, ldw=e.ff, w_gs=W * e.ff,
+                    row_dst=self.moe_row_pair, **grouped)
+        self._pending.update(pair_y=self.moe_y, pair_w=wts, top=e.top)
+        self._count(4)
 
     def _run_layers(self, T: int, x: torch.Tensor, where: dict, norm_out: bool = False) -> torch.Tensor:
         self._pending = None

@@ -446,6 +446,17 @@ int b200_latent_attn(const b200_latent_args* args, void* stream);
 int b200_latent_attn_split(const b200_latent_args* args, int32_t splits, float* scratch, void* stream);
 int64_t b200_latent_attn_scratch_bytes(int32_t T, int32_t heads, int32_t kv_rank, int32_t splits);
 
+/* Latent attention of a prompt-size chunk of ONE session on the tensor cores (16-bit modes).  The visible latents are
+ * expanded beforehand by a GEMM into per-head keys and values, kvx[r] = [W_uk c | W_uv c] of key position s0 + r
+ * (unrotated keys of head h at column h * dim, values at v_off + h * vdim; s0 <= first visible key of the chunk);
+ * the rotated key part is read from the session's cache rows (column kv_rank).  proj holds the chunk's queries (fp32,
+ * rotated part already rotated, see b200_latent_rope_append).  Sliding-window flash attention with mma.sync m16n8k16:
+ * scores and softmax in fp32, the weights enter P.V as two 16-bit terms (hi + lo).  out: 16-bit [T, heads * vdim]. */
+int b200_latent_attn_prefill(const float* proj, int32_t ldp, int32_t q_off, const void* kvx, int32_t ldkv, int32_t v_off,
+                             const void* cache, int32_t row_elems, int32_t kv_rank, void* out, int32_t ldo, int32_t T,
+                             int32_t heads, int32_t dim, int32_t rot, int32_t vdim, int32_t pos0, int32_t s0, int32_t window,
+                             float scale, int32_t dtype, int32_t pdl, void* stream);
+
 /* Router of a mixture of experts, one warp per token: scores = softmax(logits) over all experts (fp32);
  * experts form `groups` equal groups of neighbours, a group's score is its largest score, only experts of the
  * `keep` best groups can be chosen; the `top` largest allowed scores win (lowest index on ties).

@@ -51,11 +51,11 @@ def test_config_rejects_what_cannot_run():
 
 def test_cache_layout_and_span_checks():
     cfg = _cfg()
-    assert cfg.cache_layers() == [0, 2, 4] and cfg.cache_row() == 24
+    assert cfg.cache_layers() == [0, 2, 4] and cfg.cache_row() == 64
     mgr = KVCacheManager.for_span(cfg, 0, 5, torch.float32, "cpu", default_max_length=32)
     kv = mgr.allocate("s", 32)
-    assert tuple(kv.data.shape) == (3, 1, 1, 32, 24) and tuple(kv.rows(1).shape) == (32, 24)
-    assert mgr.bytes_per_token() == 3 * 24 * 4
+    assert tuple(kv.data.shape) == (3, 1, 1, 32, 64) and tuple(kv.rows(1).shape) == (32, 64)
+    assert mgr.bytes_per_token() == 3 * 64 * 4
     kv.rows(2)[5, 3] = 1.0
     assert float(kv.data[2, 0, 0, 5, 3]) == 1.0
     cfg.check_span(0, 2)

@@ -104,6 +104,7 @@ _SPANS = {}
 
 
 def span_of(name, tmp_root, dtype, max_chunk=16):
+    cap = 128 if max_chunk <= 16 else 256
     from petals_b200.models.config import resolve_config
     from petals_b200.runtime.kv_cache import KVCacheManager
     from petals_b200.runtime.layered_span import make_span
@@ -114,8 +115,8 @@ def span_of(name, tmp_root, dtype, max_chunk=16):
         d = model(name, tmp_root)[2]
         cfg = resolve_config(d)
         w = load_span(d, cfg, 0, cfg.n_layers, need_embed=True, need_head=True, dtype=dtype, device=DEV)
-        span = make_span(cfg, w, DEV, dtype, kv_capacity=128, max_batch=4, max_chunk=max_chunk)
-        mgr = KVCacheManager.for_span(cfg, 0, cfg.n_layers, dtype, DEV, default_max_length=128)
+        span = make_span(cfg, w, DEV, dtype, kv_capacity=cap, max_batch=4, max_chunk=max_chunk)
+        mgr = KVCacheManager.for_span(cfg, 0, cfg.n_layers, dtype, DEV, default_max_length=cap)
         _SPANS[key] = (span, mgr)
     return _SPANS[key]
 
@@ -125,12 +126,29 @@ def tokens_of(name, n, seed=0):
     return torch.randint(0, CONFIGS[name]["vocab"], (n,), generator=g).tolist()
 
 
-def rel_err(got, want):
-    """Root mean square of the difference over that of the expected logits, mean removed, worst row."""
+def row_errs(got, want):
+    """Per row: root mean square of the difference over that of the expected logits, mean removed."""
     d = got.double().cpu() - want.double()
     d = d - d.mean(-1, keepdim=True)
     ref = want.double() - want.double().mean(-1, keepdim=True)
-    return float((d.pow(2).mean(-1).sqrt() / ref.pow(2).mean(-1).sqrt()).max())
+    return d.pow(2).mean(-1).sqrt() / ref.pow(2).mean(-1).sqrt()
+
+
+def rel_err(got, want):
+    return float(row_errs(got, want).max())
+
+
+def assert_close_rows(got, want, dtype):
+    """fp32: every row within the tolerance.  16-bit: rounding can flip a router's close call (top-1 of a handful of
+    experts) or move a value across a clamp, which changes single rows by far more than rounding; a fault of the
+    mechanism (a window, a chunk edge, a page) would change most rows.  So: the typical row within half the
+    tolerance, at most one row in twenty beyond it."""
+    e = row_errs(got, want)
+    if dtype == torch.float32:
+        assert float(e.max()) < TOL[dtype]
+    else:
+        assert float(e.median()) < TOL[dtype] / 2 and float((e > TOL[dtype]).double().mean()) <= 0.05, \
+            (float(e.median()), float(e.max()), int((e > TOL[dtype]).sum()), e.numel())
 
 
 TOL = {torch.float32: 2e-5, torch.bfloat16: 4e-2}
@@ -414,6 +432,27 @@ def test_batches_of_unequal_requests_and_reused_sessions(name, dtype, tmp_root):
         assert rel_err(torch.cat(got[k]), want) < TOL[dtype], k
     for k in list(kvs):
         mgr.close(k)
+
+
+@pytest.mark.parametrize("dtype", MODES, ids=["fp32", "bf16"])
+@pytest.mark.parametrize("name", sorted(CONFIGS))
+def test_long_prompts_in_large_chunks(name, dtype, tmp_root):
+    """Chunks of 64 tokens (the tensor-core attention of the 16-bit mode: query tiles, key tiles and windows that
+    start in an earlier chunk), the last one partial, then decoding."""
+    span, mgr = span_of(name, tmp_root, dtype, max_chunk=64)
+    toks = tokens_of(name, 150, 11)
+    want = oracle_logits(name, tmp_root, toks)
+    kv = mgr.allocate("long", 256)
+    rows = [span.prefill(kv, ids=ids(toks[:141]), logits_at=list(range(141)))[0]]
+    for p in range(141, 150):
+        rows.append(span.decode([kv], ids=ids(toks[p:p + 1]))[0].clone())
+    assert_close_rows(torch.cat(rows), want, dtype)
+    mgr.close("long")
+    kv = mgr.allocate("long", 256)                       # a chunk that starts in the middle of a session
+    span.prefill(kv, ids=ids(toks[:37]))
+    got = span.prefill(kv, ids=ids(toks[37:150]), logits_at=list(range(150 - 37)))[0]
+    assert_close_rows(got, want[37:], dtype)
+    mgr.close("long")
 
 
 def test_a_freed_cache_is_clean_for_its_next_owner(tmp_root):
