@@ -120,6 +120,43 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(b200_simt_gemm_args a) {
     }
 }
 
+// Decode sizes (T <= 16, no grouping): one warp per output feature, the weight row streamed once with coalesced loads
+// and reused for every token - the tile kernel would leave all but a few CTAs idle and spend its time in barriers.
+constexpr int kRowsMax = 16;
+__global__ void __launch_bounds__(256) gemm_rows_kernel(b200_simt_gemm_args a) {
+    pdl_wait_prior_grid();
+    pdl_launch_dependents();
+    const int lane = threadIdx.x & 31, n = blockIdx.x * 8 + (threadIdx.x >> 5), b = blockIdx.y;
+    if (n >= a.N) return;
+    const size_t xes = a.x_dtype == B200_F32 ? 4 : 2, wes = a.w_dtype == B200_F32 ? 4 : 2;
+    const void* x = static_cast<const char*>(a.x) + (size_t)b * a.x_bs * xes;
+    const void* w = static_cast<const char*>(a.w) + ((size_t)b * a.w_bs + (size_t)n * a.ldw) * wes;
+    float acc[kRowsMax];
+#pragma unroll
+    for (int t = 0; t < kRowsMax; ++t) acc[t] = 0.f;
+#pragma unroll 4
+    for (int k = lane; k < a.K; k += 32) {
+        const float wv = ld_any(w, k, a.w_dtype);
+#pragma unroll
+        for (int t = 0; t < kRowsMax; ++t)
+            if (t < a.T) acc[t] = fmaf(ld_any(x, (size_t)t * a.ldx + k, a.x_dtype), wv, acc[t]);
+    }
+    char* ob = static_cast<char*>(a.out) + (size_t)b * a.o_bs * (a.out_dtype == B200_F32 ? 4 : 2);
+#pragma unroll
+    for (int t = 0; t < kRowsMax; ++t) {
+        if (t >= a.T) break;
+        float v = acc[t];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+        if (lane == 0) {
+            if (a.out_dtype == B200_F32)
+                reinterpret_cast<float*>(ob)[(size_t)t * a.ldo + n] = v;
+            else
+                reinterpret_cast<uint16_t*>(ob)[(size_t)t * a.ldo + n] = float_to_h16(v, a.out_dtype == B200_BF16);
+        }
+    }
+}
+
 }  // namespace b200
 
 using namespace b200;
@@ -134,6 +171,10 @@ extern "C" int b200_gemm_simt(const b200_simt_gemm_args* a, void* stream) {
     dim3 grid(row_tiles, (a->N + kTN - 1) / kTN, batch);
     if (grid.y > 65535 || grid.z > 65535) return fail(B200_ELIMIT, "b200_gemm_simt: grid too large");
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (a->T <= kRowsMax && !a->group_off && !a->w2 && !a->row_src && !a->row_dst && !a->row_scale && batch <= 65535) {
+        B200_CUDA_CHECK(launch(gemm_rows_kernel, dim3((a->N + 7) / 8, batch), dim3(256), 0, s, a->pdl != 0, *a));
+        return B200_OK;
+    }
     if (a->w2)
         B200_CUDA_CHECK(launch(gemm_simt_kernel<true>, grid, dim3(256), 0, s, a->pdl != 0, *a));
     else

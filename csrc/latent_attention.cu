@@ -102,17 +102,35 @@ __global__ void __launch_bounds__(256) latent_attn_kernel(b200_latent_args a, in
     const bool f32 = a.cache_dtype == B200_F32;
     const int bf = a.cache_dtype == B200_BF16;
     const char* base = static_cast<const char*>(latent_row(a, t, 0));
+    const bool vec16 = !f32 && E % 8 == 0 && a.row_elems % 8 == 0 && (reinterpret_cast<uintptr_t>(base) & 15) == 0;
     float m = -INFINITY, l = 0.f, acc[NPER];
 #pragma unroll
     for (int i = 0; i < NPER; ++i) acc[i] = 0.f;
     for (int j0 = lo; j0 <= hi; j0 += kChunk) {
         const int n = hi - j0 + 1 < kChunk ? hi - j0 + 1 : kChunk;
         __syncthreads();                                     // previous chunk fully consumed (and qs written)
-        for (int e = tid; e < n * E; e += 256) {
-            const int j = e / E, d = e - j * E;
-            const size_t g = (size_t)(j0 + j) * a.row_elems + d;
-            kc[j * ldk + d] = f32 ? reinterpret_cast<const float*>(base)[g]
-                                  : h16_to_float(reinterpret_cast<const uint16_t*>(base)[g], bf);
+        if (vec16) {          // 16-byte loads, several in flight per thread (a dependent 2-byte load per element is
+            const int cpr = E / 8;   // latency-bound: ~70 us per 32 keys on a cold cache)
+#pragma unroll 4
+            for (int e = tid; e < n * cpr; e += 256) {
+                const int j = e / cpr, d = (e - j * cpr) * 8;
+                const uint4 v = *reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(base) + (size_t)(j0 + j) * a.row_elems + d);
+                const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+                float* dst = kc + j * ldk + d;
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    dst[2 * i] = h16_to_float((uint16_t)(w[i] & 0xffff), bf);
+                    dst[2 * i + 1] = h16_to_float((uint16_t)(w[i] >> 16), bf);
+                }
+            }
+        } else {
+#pragma unroll 4
+            for (int e = tid; e < n * E; e += 256) {
+                const int j = e / E, d = e - j * E;
+                const size_t g = (size_t)(j0 + j) * a.row_elems + d;
+                kc[j * ldk + d] = f32 ? reinterpret_cast<const float*>(base)[g]
+                                      : h16_to_float(reinterpret_cast<const uint16_t*>(base)[g], bf);
+            }
         }
         __syncthreads();
         if (!live) continue;
@@ -177,7 +195,8 @@ __global__ void __launch_bounds__(256) latent_attn_kernel(b200_latent_args a, in
     }
 }
 
-// One warp per (token, head): the shares' (acc, m, l) merged in index order, then normalised.
+// One warp per (token, head): the shares' (acc, m, l) merged in index order, then normalised.  Lane s holds the weight
+// exp(m_s - m) of share s (splits <= 32).
 __global__ void __launch_bounds__(128) latent_merge_kernel(const float* __restrict__ part, float* __restrict__ out, int ldout,
                                                           int T, int heads, int R, int splits) {
     pdl_wait_prior_grid();
@@ -186,21 +205,23 @@ __global__ void __launch_bounds__(128) latent_merge_kernel(const float* __restri
     if (w >= T * heads) return;
     const int t = w / heads, h = w - t * heads;
     const float* p = part + (size_t)w * splits * (R + 2);
-    float m = -INFINITY;
-    for (int s = 0; s < splits; ++s) m = fmaxf(m, p[(size_t)s * (R + 2) + R]);
+    const float ms = lane < splits ? p[(size_t)lane * (R + 2) + R] : -INFINITY;
+    const float ls = lane < splits ? p[(size_t)lane * (R + 2) + R + 1] : 0.f;
+    float m = ms;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    const float ws = ms > -INFINITY ? expf(ms - m) : 0.f;
     float l = 0.f;
-    for (int s = 0; s < splits; ++s) {
-        const float ms = p[(size_t)s * (R + 2) + R];
-        if (ms > -INFINITY) l += p[(size_t)s * (R + 2) + R + 1] * expf(ms - m);
-    }
+    for (int s = 0; s < splits; ++s) l += __shfl_sync(0xffffffffu, ls * ws, s);      // index order
     const float inv = 1.0f / l;
-    for (int d = lane; d < R; d += 32) {
+    for (int d0 = 0; d0 < R; d0 += 32) {
+        const int d = d0 + lane;
         float acc = 0.f;
         for (int s = 0; s < splits; ++s) {
-            const float ms = p[(size_t)s * (R + 2) + R];
-            if (ms > -INFINITY) acc += p[(size_t)s * (R + 2) + d] * expf(ms - m);
+            const float wv = __shfl_sync(0xffffffffu, ws, s);
+            if (d < R && wv != 0.f) acc += wv * p[(size_t)s * (R + 2) + d];
         }
-        out[(size_t)t * ldout + (size_t)h * R + d] = acc * inv;
+        if (d < R) out[(size_t)t * ldout + (size_t)h * R + d] = acc * inv;
     }
 }
 
@@ -250,7 +271,7 @@ extern "C" int b200_latent_attn(const b200_latent_args* a, void* stream) {
 
 extern "C" int b200_latent_attn_split(const b200_latent_args* a, int32_t splits, float* scratch, void* stream) {
     if (int rc = check_latent(a, "b200_latent_attn")) return rc;
-    if (splits < 1 || splits > 64 || (splits > 1 && !scratch)) return fail(B200_EINVAL, "b200_latent_attn: bad splits %d", splits);
+    if (splits < 1 || splits > 32 || (splits > 1 && !scratch)) return fail(B200_EINVAL, "b200_latent_attn: bad splits %d", splits);
     if (!a->q_abs || !a->out || a->window <= 0) return fail(B200_EINVAL, "b200_latent_attn: q_abs / out / window missing");
     const int E = a->kv_rank + a->rot;
     const size_t smem = ((size_t)kHeadsPerBlock * E + (size_t)kChunk * (E | 1)) * sizeof(float);

@@ -19,6 +19,7 @@ struct LatentMmaParams {
     int T, heads, dim, rot, vdim, pos0, s0, window;
     float scale;
     int is_bf16;
+    int vec;                  // sizes and addresses allow 16-byte tile loads
 };
 
 __device__ __forceinline__ void mma_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1, int is_bf16) {
@@ -52,6 +53,7 @@ __global__ void __launch_bounds__(128) latent_attn_mma_kernel(LatentMmaParams p)
     uint16_t* Ks = Qs + kQT * ldq;               // [64][ldq]
     uint16_t* Vt = Ks + kKT * ldq;               // [NV * 8][ldv]   (transposed: value column major)
     const int bf = p.is_bf16;
+    const bool vec = p.vec != 0;
     // ---- Q tile: fp32 -> 16-bit, zero beyond T and beyond dq
     for (int e = tid; e < kQT * dqp; e += 128) {
         const int r = e / dqp, d = e - r * dqp;
@@ -71,24 +73,56 @@ __global__ void __launch_bounds__(128) latent_attn_mma_kernel(LatentMmaParams p)
     for (int k0 = kmin; k0 <= plast; k0 += kKT) {
         __syncthreads();                                                         // the previous tile is consumed (Q written)
         // ---- K tile [64][dq]: unrotated part of this head from kvx, rotated part from the cache row; V tile transposed
-        for (int e = tid; e < kKT * dqp; e += 128) {
-            const int j = e / dqp, d = e - j * dqp;
-            const int kp = k0 + j;
-            uint16_t v = 0;
-            if (kp <= plast) {
-                if (d < p.dim)
-                    v = p.kvx[(size_t)(kp - p.s0) * p.ldkv + h * p.dim + d];
-                else if (d < dq)
-                    v = p.cache[(size_t)kp * p.row_elems + p.kv_rank + (d - p.dim)];
+        if (vec) {       // every 8-element group lies in one source and is 16-byte aligned there
+            const int cpr = dqp / 8;
+#pragma unroll 2
+            for (int e = tid; e < kKT * cpr; e += 128) {
+                const int j = e / cpr, d = (e - j * cpr) * 8;
+                const int kp = k0 + j;
+                uint4 v = make_uint4(0, 0, 0, 0);
+                if (kp <= plast) {
+                    if (d < p.dim)
+                        v = *reinterpret_cast<const uint4*>(p.kvx + (size_t)(kp - p.s0) * p.ldkv + h * p.dim + d);
+                    else if (d < dq)
+                        v = *reinterpret_cast<const uint4*>(p.cache + (size_t)kp * p.row_elems + p.kv_rank + (d - p.dim));
+                }
+                *reinterpret_cast<uint4*>(Ks + j * ldq + d) = v;
             }
-            Ks[j * ldq + d] = v;
-        }
-        for (int e = tid; e < kKT * NV * 8; e += 128) {
-            const int j = e / (NV * 8), c = e - j * (NV * 8);
-            const int kp = k0 + j;
-            uint16_t v = 0;
-            if (kp <= plast && c < p.vdim) v = p.kvx[(size_t)(kp - p.s0) * p.ldkv + p.v_off + h * p.vdim + c];
-            Vt[c * ldv + j] = v;
+            // lanes run along the keys: the transposed stores of a warp fall into consecutive halves of one row
+#pragma unroll 2
+            for (int e = tid; e < kKT * NV; e += 128) {
+                const int j = e % kKT, c = (e / kKT) * 8;
+                const int kp = k0 + j;
+                uint4 v = make_uint4(0, 0, 0, 0);
+                if (kp <= plast && c < p.vdim)
+                    v = *reinterpret_cast<const uint4*>(p.kvx + (size_t)(kp - p.s0) * p.ldkv + p.v_off + h * p.vdim + c);
+                const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    Vt[(c + 2 * i) * ldv + j] = (uint16_t)(w[i] & 0xffff);
+                    Vt[(c + 2 * i + 1) * ldv + j] = (uint16_t)(w[i] >> 16);
+                }
+            }
+        } else {
+            for (int e = tid; e < kKT * dqp; e += 128) {
+                const int j = e / dqp, d = e - j * dqp;
+                const int kp = k0 + j;
+                uint16_t v = 0;
+                if (kp <= plast) {
+                    if (d < p.dim)
+                        v = p.kvx[(size_t)(kp - p.s0) * p.ldkv + h * p.dim + d];
+                    else if (d < dq)
+                        v = p.cache[(size_t)kp * p.row_elems + p.kv_rank + (d - p.dim)];
+                }
+                Ks[j * ldq + d] = v;
+            }
+            for (int e = tid; e < kKT * NV * 8; e += 128) {
+                const int j = e / (NV * 8), c = e - j * (NV * 8);
+                const int kp = k0 + j;
+                uint16_t v = 0;
+                if (kp <= plast && c < p.vdim) v = p.kvx[(size_t)(kp - p.s0) * p.ldkv + p.v_off + h * p.vdim + c];
+                Vt[c * ldv + j] = v;
+            }
         }
         __syncthreads();
         // ---- S = Q K^T for this warp's 16 rows
@@ -225,6 +259,9 @@ extern "C" int b200_latent_attn_prefill(const float* proj, int32_t ldp, int32_t 
     p.ldp = ldp; p.q_off = q_off; p.ldkv = ldkv; p.v_off = v_off; p.row_elems = row_elems; p.kv_rank = kv_rank; p.ldo = ldo;
     p.T = T; p.heads = heads; p.dim = dim; p.rot = rot; p.vdim = vdim; p.pos0 = pos0; p.s0 = s0; p.window = window;
     p.scale = scale; p.is_bf16 = dtype == B200_BF16 ? 1 : 0;
+    p.vec = (dim % 8 == 0 && rot % 8 == 0 && vdim % 8 == 0 && ldkv % 8 == 0 && v_off % 8 == 0 && row_elems % 8 == 0 &&
+             kv_rank % 8 == 0 && (reinterpret_cast<uintptr_t>(kvx) & 15) == 0 && (reinterpret_cast<uintptr_t>(cache) & 15) == 0)
+                ? 1 : 0;
     const int dqp = (dim + rot + 15) / 16 * 16;
     const int nv = (vdim + 7) / 8;
     const int NV = nv <= 4 ? 4 : nv <= 8 ? 8 : nv <= 16 ? 16 : 32;
