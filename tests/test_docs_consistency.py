@@ -37,7 +37,8 @@ def test_cli_flags_named_in_the_docs_exist():
              "--import-source", "--page", "--csv", "--kill_stage", "--kill_at_token", "--hard", "--out", "--clients",
              "--yes", "--metrics", "--standalone", "--local-addr", "--base_port", "--port_base", "--graph-profiling",
              "--sessions", "--group", "--tp-mode", "--prompt-len", "--linger_ms", "--soft", "--no-index",
-             "--no-build-isolation", "--find-links", "--target", "--no-deps", "--log-file", "--launch-skip"}
+             "--no-build-isolation", "--find-links", "--target", "--no-deps", "--log-file", "--launch-skip",
+             "--designs", "--design-sizes", "--design-only", "--unit-set", "--dtype", "--max-tokens"}
     missing = {}
     for doc in DOCS:
         for flag in set(re.findall(r"(?<![\w-])--[a-z][a-z0-9_-]+", _read(doc))):
