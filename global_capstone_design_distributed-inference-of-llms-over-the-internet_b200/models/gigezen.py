@@ -28,7 +28,7 @@ class LatentAttentionSpec:
     rot_dim: int                # rotated query/key dimensions per head (the key part is shared by all heads)
     vdim: int
     kv_rank: int
-    window: int                 # position i sees j with 0 <= i - j < window
+    window: int                 # causal band: query i attends to the keys j in (i - window, i]
     scale: float
     rope_base: float
     rope_dims: int              # rotated dimensions of the rot part (pairs i, i + rope_dims/2)

@@ -436,8 +436,8 @@ typedef struct b200_latent_args {
     int32_t pdl, reserved;
 } b200_latent_args;
 int b200_latent_rope_append(const b200_latent_args* args, void* stream);
-/* Step 2: scores s(j) = (q_abs . c_j + q_rot . kr_j) * scale over the cached rows j with 0 <= pos - j < window,
- * softmax in fp32, out = sum_j p_j c_j.  All heads of a token share the cached rows (one block = one token x 8 heads,
+/* Step 2: for the token at position pos, the keys are the cached rows j in (pos - window, pos]; score
+ * s(j) = (q_abs . c_j + q_rot . kr_j) * scale, softmax in fp32, out = sum_j p_j c_j.  All heads of a token share the cached rows (one block = one token x 8 heads,
  * keys staged through shared memory 32 at a time). */
 int b200_latent_attn(const b200_latent_args* args, void* stream);
 /* The same with the window's keys of every token divided over `splits` blocks (decode sizes, where tokens x heads alone
@@ -457,10 +457,11 @@ int b200_latent_attn_prefill(const float* proj, int32_t ldp, int32_t q_off, cons
                              int32_t heads, int32_t dim, int32_t rot, int32_t vdim, int32_t pos0, int32_t s0, int32_t window,
                              float scale, int32_t dtype, int32_t pdl, void* stream);
 
-/* Router of a mixture of experts, one warp per token: scores = softmax(logits) over all experts (fp32);
- * experts form `groups` equal groups of neighbours, a group's score is its largest score, only experts of the
- * `keep` best groups can be chosen; the `top` largest allowed scores win (lowest index on ties).
- * ids [T, top] int32, weights [T, top] fp32 = the chosen scores (renorm != 0: divided by their sum). */
+/* Router of a mixture of experts, one warp per token.  s = softmax(logits) over all `experts` (fp32).  Group-limited
+ * top-k: consecutive experts are partitioned into `groups` blocks, a block is ranked by max(s) inside it, and the
+ * candidates are the members of the `keep` highest-ranked blocks; among the candidates the `top` highest s are taken
+ * (lowest index on ties).  ids [T, top] int32; weights [T, top] fp32 = s of the taken experts as it is
+ * (renorm != 0: divided by their sum). */
 int b200_moe_route(const float* logits, int32_t ld, int32_t T, int32_t experts, int32_t groups, int32_t keep, int32_t top,
                    int32_t renorm, int32_t* ids, float* weights, int32_t pdl, void* stream);
 /* Sorts the T*top (token, slot) pairs by expert (single block): group_off [experts + 1], row_pair [T*top] (pair

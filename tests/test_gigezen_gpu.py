@@ -543,3 +543,22 @@ def test_trace_replay_steps(tmp_root, tmp_path):
     assert r2 is None
     r3 = rp.step([{"id": "y", "tokens": ta[:4], "want": [3]}, {"id": "x", "tokens": ta[17:20], "want": [2]}], ["x", "y"])
     assert rel_err(r3, torch.stack([wa[3], wa[19]])) < 2e-5
+
+
+def test_command_line_generates_from_a_model_folder(tmp_root):
+    """``python -m src.main --inbox`` on a Gigezen folder: registry, loader, engine, greedy decoding, byte tokenizer."""
+    import subprocess
+    import sys
+
+    name = "wide"
+    cfg, w, d, _ = model(name, tmp_root)
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", MASTER_PORT="29631", RANK="0", WORLD_SIZE="1", LOCAL_RANK="0")
+    r = subprocess.run([sys.executable, "-m", "src.main", "--inbox", "--stage", "0", "--model", d, "--splits", "", "--dtype", "fp32",
+                        "--temperature", "0", "--max_new_tokens", "6", "--prompt", "abc"], cwd=root, env=env,
+                       capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stderr[-2000:]
+    prompt = [(3 + b) % cfg["vocab"] for b in b"abc"]
+    want = O.greedy(cfg, w, prompt, 6)
+    text = bytearray((t - 3) if 0 <= t - 3 < 256 else ord("?") for t in want).decode("utf-8", errors="replace")
+    assert "GENERATED: " + text in r.stdout, (r.stdout[-500:], want)
