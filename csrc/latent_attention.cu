@@ -195,34 +195,31 @@ __global__ void __launch_bounds__(256) latent_attn_kernel(b200_latent_args a, in
     }
 }
 
-// One warp per (token, head): the shares' (acc, m, l) merged in index order, then normalised.  Lane s holds the weight
-// exp(m_s - m) of share s (splits <= 32).
+// One warp per (token, head, 32 output columns): the shares' (acc, m, l) merged in index order, then normalised.
+// Lane s holds the weight exp(m_s - m) of share s (splits <= 32).
 __global__ void __launch_bounds__(128) latent_merge_kernel(const float* __restrict__ part, float* __restrict__ out, int ldout,
                                                           int T, int heads, int R, int splits) {
     pdl_wait_prior_grid();
     pdl_launch_dependents();
+    const int slices = (R + 31) / 32;
     const int w = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
-    if (w >= T * heads) return;
-    const int t = w / heads, h = w - t * heads;
-    const float* p = part + (size_t)w * splits * (R + 2);
+    if (w >= T * heads * slices) return;
+    const int th = w / slices, d = (w - th * slices) * 32 + lane;
+    const int t = th / heads, h = th - t * heads;
+    const float* p = part + (size_t)th * splits * (R + 2);
     const float ms = lane < splits ? p[(size_t)lane * (R + 2) + R] : -INFINITY;
     const float ls = lane < splits ? p[(size_t)lane * (R + 2) + R + 1] : 0.f;
     float m = ms;
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
     const float ws = ms > -INFINITY ? expf(ms - m) : 0.f;
-    float l = 0.f;
-    for (int s = 0; s < splits; ++s) l += __shfl_sync(0xffffffffu, ls * ws, s);      // index order
-    const float inv = 1.0f / l;
-    for (int d0 = 0; d0 < R; d0 += 32) {
-        const int d = d0 + lane;
-        float acc = 0.f;
-        for (int s = 0; s < splits; ++s) {
-            const float wv = __shfl_sync(0xffffffffu, ws, s);
-            if (d < R && wv != 0.f) acc += wv * p[(size_t)s * (R + 2) + d];
-        }
-        if (d < R) out[(size_t)t * ldout + (size_t)h * R + d] = acc * inv;
+    float l = 0.f, acc = 0.f;
+    for (int s = 0; s < splits; ++s) {                                               // index order
+        const float wv = __shfl_sync(0xffffffffu, ws, s);
+        l += __shfl_sync(0xffffffffu, ls, s) * wv;
+        if (d < R && wv != 0.f) acc += wv * p[(size_t)s * (R + 2) + d];
     }
+    if (d < R) out[(size_t)t * ldout + (size_t)h * R + d] = acc / l;
 }
 
 template <int NPER>
@@ -232,7 +229,7 @@ static int launch_attn(const b200_latent_args* a, size_t smem, cudaStream_t s, i
     dim3 grid(a->T, (a->heads + kHeadsPerBlock - 1) / kHeadsPerBlock, splits);
     B200_CUDA_CHECK(launch(latent_attn_kernel<NPER>, grid, dim3(256), smem, s, a->pdl != 0, *a, splits, part));
     if (splits > 1)
-        B200_CUDA_CHECK(launch(latent_merge_kernel, dim3((a->T * a->heads + 3) / 4), dim3(128), 0, s, a->pdl != 0,
+        B200_CUDA_CHECK(launch(latent_merge_kernel, dim3((a->T * a->heads * ((a->kv_rank + 31) / 32) + 3) / 4), dim3(128), 0, s, a->pdl != 0,
                                (const float*)part, a->out, a->ldout, a->T, a->heads, a->kv_rank, splits));
     return B200_OK;
 }

@@ -4,7 +4,8 @@
 //   S = [q_unrotated | q_rotated] . [k_unrotated(head) | k_rotated(shared)]^T   mma.sync m16n8k16, 16-bit in, fp32 out
 //   online softmax in fp32 registers
 //   O += P . V with P split into two 16-bit terms (hi + lo), so the weights enter the product with ~16 bits
-// One block = 64 consecutive queries of one head (4 warps x 16 rows), keys in tiles of 64.
+// One block = 64 consecutive queries of one head (4 warps x 16 rows), keys in tiles of 64; the next key / value tile is
+// fetched by cp.async into a second shared-memory buffer while the tensor cores work on the current one.
 #include "common.h"
 #include "ptx.cuh"
 
@@ -39,6 +40,18 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi, int is_bf16) {
 
 constexpr int kQT = 64, kKT = 64;
 
+// 16-byte asynchronous copy global -> shared; bytes = 0 writes zeros (the source is not read)
+__device__ __forceinline__ void cp_async16(void* dst, const void* src, int bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(smem_u32(dst)), "l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory"); }
+// two 8x8 16-bit matrices, transposed on the way: lane l < 16 names row l % 8 of matrix l / 8
+__device__ __forceinline__ void ldmatrix_x2_trans(uint32_t& r0, uint32_t& r1, const void* row) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];\n" : "=r"(r0), "=r"(r1) : "r"(smem_u32(row)));
+}
+
 // NV = value n-tiles of 8 columns (vdim <= 8 * NV)
 template <int NV>
 __global__ void __launch_bounds__(128) latent_attn_mma_kernel(LatentMmaParams p) {
@@ -48,10 +61,10 @@ __global__ void __launch_bounds__(128) latent_attn_mma_kernel(LatentMmaParams p)
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, tq = lane & 3;
     const int h = blockIdx.y, q0 = blockIdx.x * kQT;
     const int dq = p.dim + p.rot, dqp = (dq + 15) / 16 * 16, ldq = dqp + 8;      // +8 halves: rows land on different banks
-    const int ldv = kKT + 8;
+    const int ldv = NV * 8 + 8;
     uint16_t* Qs = smem16;                       // [64][ldq]
-    uint16_t* Ks = Qs + kQT * ldq;               // [64][ldq]
-    uint16_t* Vt = Ks + kKT * ldq;               // [NV * 8][ldv]   (transposed: value column major)
+    uint16_t* Kb = Qs + kQT * ldq;               // 2 x [64][ldq]
+    uint16_t* Vb = Kb + 2 * kKT * ldq;           // 2 x [64][ldv]   (key major; transposed by ldmatrix on the way out)
     const int bf = p.is_bf16;
     const bool vec = p.vec != 0;
     // ---- Q tile: fp32 -> 16-bit, zero beyond T and beyond dq
@@ -70,38 +83,33 @@ __global__ void __launch_bounds__(128) latent_attn_mma_kernel(LatentMmaParams p)
     for (int i = 0; i < NV; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
     float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;                    // rows g and g + 8 of this warp's 16
     const int qp0 = P0 + warp * 16 + g, qp1 = qp0 + 8;
-    for (int k0 = kmin; k0 <= plast; k0 += kKT) {
-        __syncthreads();                                                         // the previous tile is consumed (Q written)
-        // ---- K tile [64][dq]: unrotated part of this head from kvx, rotated part from the cache row; V tile transposed
+    auto load_tile = [&](int buf, int k0) {
+        uint16_t* Ks = Kb + buf * kKT * ldq;
+        uint16_t* Vs = Vb + buf * kKT * ldv;
         if (vec) {       // every 8-element group lies in one source and is 16-byte aligned there
             const int cpr = dqp / 8;
-#pragma unroll 2
             for (int e = tid; e < kKT * cpr; e += 128) {
                 const int j = e / cpr, d = (e - j * cpr) * 8;
                 const int kp = k0 + j;
-                uint4 v = make_uint4(0, 0, 0, 0);
+                const uint16_t* src = p.kvx;
+                int bytes = 0;
                 if (kp <= plast) {
-                    if (d < p.dim)
-                        v = *reinterpret_cast<const uint4*>(p.kvx + (size_t)(kp - p.s0) * p.ldkv + h * p.dim + d);
-                    else if (d < dq)
-                        v = *reinterpret_cast<const uint4*>(p.cache + (size_t)kp * p.row_elems + p.kv_rank + (d - p.dim));
+                    if (d < p.dim) {
+                        src = p.kvx + (size_t)(kp - p.s0) * p.ldkv + h * p.dim + d;
+                        bytes = 16;
+                    } else if (d < dq) {
+                        src = p.cache + (size_t)kp * p.row_elems + p.kv_rank + (d - p.dim);
+                        bytes = 16;
+                    }
                 }
-                *reinterpret_cast<uint4*>(Ks + j * ldq + d) = v;
+                cp_async16(Ks + j * ldq + d, src, bytes);
             }
-            // lanes run along the keys: the transposed stores of a warp fall into consecutive halves of one row
-#pragma unroll 2
             for (int e = tid; e < kKT * NV; e += 128) {
-                const int j = e % kKT, c = (e / kKT) * 8;
+                const int j = e / NV, c = (e - j * NV) * 8;
                 const int kp = k0 + j;
-                uint4 v = make_uint4(0, 0, 0, 0);
-                if (kp <= plast && c < p.vdim)
-                    v = *reinterpret_cast<const uint4*>(p.kvx + (size_t)(kp - p.s0) * p.ldkv + p.v_off + h * p.vdim + c);
-                const uint32_t w[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    Vt[(c + 2 * i) * ldv + j] = (uint16_t)(w[i] & 0xffff);
-                    Vt[(c + 2 * i + 1) * ldv + j] = (uint16_t)(w[i] >> 16);
-                }
+                const bool in = kp <= plast && c < p.vdim;
+                const uint16_t* src = in ? p.kvx + (size_t)(kp - p.s0) * p.ldkv + p.v_off + h * p.vdim + c : p.kvx;
+                cp_async16(Vs + j * ldv + c, src, in ? 16 : 0);
             }
         } else {
             for (int e = tid; e < kKT * dqp; e += 128) {
@@ -121,10 +129,23 @@ __global__ void __launch_bounds__(128) latent_attn_mma_kernel(LatentMmaParams p)
                 const int kp = k0 + j;
                 uint16_t v = 0;
                 if (kp <= plast && c < p.vdim) v = p.kvx[(size_t)(kp - p.s0) * p.ldkv + p.v_off + h * p.vdim + c];
-                Vt[c * ldv + j] = v;
+                Vs[j * ldv + c] = v;
             }
         }
-        __syncthreads();
+        cp_async_commit();
+    };
+    load_tile(0, kmin);
+    int buf = 0;
+    for (int k0 = kmin; k0 <= plast; k0 += kKT, buf ^= 1) {
+        if (k0 + kKT <= plast) {                                                 // fetch the next tile under this one's math
+            load_tile(buf ^ 1, k0 + kKT);
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
+        }
+        __syncthreads();                                                         // tile `buf` (and Q) visible to all warps
+        const uint16_t* Ks = Kb + buf * kKT * ldq;
+        const uint16_t* Vs = Vb + buf * kKT * ldv;
         // ---- S = Q K^T for this warp's 16 rows
         float s[8][4];
 #pragma unroll
@@ -208,12 +229,13 @@ __global__ void __launch_bounds__(128) latent_attn_mma_kernel(LatentMmaParams p)
             }
 #pragma unroll
             for (int i = 0; i < NV; ++i) {
-                const uint16_t* vrow = Vt + (i * 8 + g) * ldv + ks * 16 + 2 * tq;
-                const uint32_t b0 = *reinterpret_cast<const uint32_t*>(vrow), b1 = *reinterpret_cast<const uint32_t*>(vrow + 8);
+                uint32_t b0, b1;
+                ldmatrix_x2_trans(b0, b1, Vs + (ks * 16 + (lane & 15)) * ldv + i * 8);
                 mma_16816(o[i], ah, b0, b1, bf);
                 mma_16816(o[i], alo, b0, b1, bf);
             }
         }
+        __syncthreads();                                                         // all warps are done with tile `buf`
     }
     // ---- normalise and store (16-bit)
     const int r0 = q0 + warp * 16 + g, r1 = r0 + 8;
@@ -265,7 +287,7 @@ extern "C" int b200_latent_attn_prefill(const float* proj, int32_t ldp, int32_t 
     const int dqp = (dim + rot + 15) / 16 * 16;
     const int nv = (vdim + 7) / 8;
     const int NV = nv <= 4 ? 4 : nv <= 8 ? 8 : nv <= 16 ? 16 : 32;
-    const size_t smem = ((size_t)(kQT + kKT) * (dqp + 8) + (size_t)NV * 8 * (kKT + 8)) * sizeof(uint16_t);
+    const size_t smem = ((size_t)(kQT + 2 * kKT) * (dqp + 8) + (size_t)2 * kKT * (NV * 8 + 8)) * sizeof(uint16_t);
     if (smem > 200 * 1024) return fail(B200_ELIMIT, "b200_latent_attn_prefill: dim + rot = %d exceeds shared memory", dim + rot);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     switch (NV) {
