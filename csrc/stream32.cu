@@ -29,6 +29,22 @@ __global__ void __launch_bounds__(128) embed_f32_kernel(const long long* __restr
     for (int c = threadIdx.x; c < width; c += blockDim.x) out[(size_t)t * ldo + c] = load_elem(table, (size_t)id * width + c, dtype);
 }
 
+__global__ void __launch_bounds__(128) embed_pos_f32_kernel(const long long* __restrict__ ids, const void* __restrict__ table,
+                                                           const void* __restrict__ pos_table, int dtype,
+                                                           const int* __restrict__ pos, int pos0, float* __restrict__ out,
+                                                           int T, int width, int ldo, int vocab, int max_pos) {
+    pdl_wait_prior_grid();
+    pdl_launch_dependents();
+    const int t = blockIdx.x;
+    if (t >= T) return;
+    long long id = ids[t];
+    id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);
+    int p = pos ? pos[t] : pos0 + t;
+    p = p < 0 ? 0 : (p >= max_pos ? max_pos - 1 : p);
+    for (int c = threadIdx.x; c < width; c += blockDim.x)
+        out[(size_t)t * ldo + c] = load_elem(table, (size_t)id * width + c, dtype) + load_elem(pos_table, (size_t)p * width + c, dtype);
+}
+
 // ------------------------------------------------------------------ residual update + RMS norm
 // One block per token.  The updated row is kept in shared memory between the two passes.
 __global__ void __launch_bounds__(256) add_rms_norm_kernel(b200_add_norm_args a) {
@@ -56,7 +72,7 @@ __global__ void __launch_bounds__(256) add_rms_norm_kernel(b200_add_norm_args a)
             any = true;
         }
         if (any) {
-            v += add;
+            v += a.add_scale * add;
             x[c] = v;
         }
         row[c] = v;
@@ -94,9 +110,80 @@ __global__ void __launch_bounds__(256) glu_clamp_kernel(const float* __restrict_
     }
 }
 
+// ------------------------------------------------------------------ piecewise activation with two learned numbers
+__device__ __forceinline__ float softplus_f(float x) { return fmaxf(x, 0.f) + log1pf(expf(-fabsf(x))); }
+
+__global__ void __launch_bounds__(256) xielu_kernel(const float* __restrict__ z, int ld, const float* __restrict__ params,
+                                                   float lin, float neg_base, void* __restrict__ act, int ldo, int out_dtype,
+                                                   int T, int ff) {
+    pdl_wait_prior_grid();
+    pdl_launch_dependents();
+    const float ap = softplus_f(params[0]), an = neg_base + softplus_f(params[1]);
+    const size_t n = (size_t)T * ff;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        const int t = (int)(i / ff), c = (int)(i - (size_t)t * ff);
+        const float v = z[(size_t)t * ld + c];
+        const float y = v > 0.f ? fmaf(ap * v, v, lin * v) : fmaf(an, expm1f(v) - v, lin * v);
+        store_elem(act, (size_t)t * ldo + c, y, out_dtype);
+    }
+}
+
+// ------------------------------------------------------------------ gated RMS norm per head (one warp per token and head)
+__global__ void __launch_bounds__(128) gated_head_norm_kernel(const float* __restrict__ o, int ldo, const float* __restrict__ gate,
+                                                             int ldg, const float* __restrict__ gain, void* __restrict__ out,
+                                                             int ldout, int out_dtype, int T, int heads, int vdim, float eps) {
+    pdl_wait_prior_grid();
+    pdl_launch_dependents();
+    const int w = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (w >= T * heads) return;
+    const int t = w / heads, h = w - t * heads;
+    const float* src = o + (size_t)t * ldo + (size_t)h * vdim;
+    const float* g = gate + (size_t)t * ldg + (size_t)h * vdim;
+    float ss = 0.f;
+    for (int d = lane; d < vdim; d += 32) ss = fmaf(src[d], src[d], ss);
+#pragma unroll
+    for (int s = 16; s > 0; s >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, s);
+    const float rstd = 1.0f / sqrtf(ss / (float)vdim + eps);
+    for (int d = lane; d < vdim; d += 32) {
+        const float z = g[d];
+        store_elem(out, (size_t)t * ldout + (size_t)h * vdim + d, src[d] * rstd * gain[d] * (z / (1.0f + expf(-z))), out_dtype);
+    }
+}
+
 }  // namespace b200
 
 using namespace b200;
+
+extern "C" int b200_embed_pos_f32(const void* ids, const void* table, const void* pos_table, int32_t table_dtype,
+                                  const int32_t* pos, int32_t pos0, float* out, int32_t T, int32_t width, int32_t ldo,
+                                  int32_t vocab, int32_t max_pos, int32_t pdl, void* stream) {
+    if (!ids || !table || !pos_table || !out || T <= 0 || width <= 0 || max_pos <= 0)
+        return fail(B200_EINVAL, "b200_embed_pos_f32: bad argument");
+    B200_CUDA_CHECK(launch(embed_pos_f32_kernel, dim3(T), dim3(128), 0, static_cast<cudaStream_t>(stream), pdl != 0,
+                           static_cast<const long long*>(ids), table, pos_table, table_dtype, pos, pos0, out, T, width, ldo,
+                           vocab, max_pos));
+    return B200_OK;
+}
+
+extern "C" int b200_xielu(const float* z, int32_t ld, const float* params, float lin, float neg_base, void* act, int32_t ldo,
+                          int32_t out_dtype, int32_t T, int32_t ff, int32_t pdl, void* stream) {
+    if (!z || !params || !act || T <= 0 || ff <= 0) return fail(B200_EINVAL, "b200_xielu: bad argument");
+    const size_t n = (size_t)T * ff;
+    const int blocks = (int)((n + 255) / 256 < 4096 ? (n + 255) / 256 : 4096);
+    B200_CUDA_CHECK(launch(xielu_kernel, dim3(blocks), dim3(256), 0, static_cast<cudaStream_t>(stream), pdl != 0, z, ld, params,
+                           lin, neg_base, act, ldo, out_dtype, T, ff));
+    return B200_OK;
+}
+
+extern "C" int b200_gated_head_norm(const float* o, int32_t ldo, const float* gate, int32_t ldg, const float* gain, void* out,
+                                    int32_t ldout, int32_t out_dtype, int32_t T, int32_t heads, int32_t vdim, float eps,
+                                    int32_t pdl, void* stream) {
+    if (!o || !gate || !gain || !out || T <= 0 || heads <= 0 || vdim <= 0)
+        return fail(B200_EINVAL, "b200_gated_head_norm: bad argument");
+    B200_CUDA_CHECK(launch(gated_head_norm_kernel, dim3((T * heads + 3) / 4), dim3(128), 0, static_cast<cudaStream_t>(stream),
+                           pdl != 0, o, ldo, gate, ldg, gain, out, ldout, out_dtype, T, heads, vdim, eps));
+    return B200_OK;
+}
 
 extern "C" int b200_embed_f32(const void* ids, const void* table, int32_t table_dtype, float* out, int32_t T, int32_t width,
                               int32_t ldo, int32_t vocab, int32_t pdl, void* stream) {

@@ -1,4 +1,4 @@
-"""Architecture descriptions for the supported families (Llama, GPT-2, and the layer-list design Gigezen).
+"""Architecture descriptions for the supported families (Llama, GPT-2, and the layer-list designs Gigezen and Seledra).
 
 The reference accepts any HF model name but only runs Llama-family models
 (src/llama_partition.py:81-83) while advertising GPT-2 (README / run_all.py
@@ -91,6 +91,10 @@ def from_hf_dict(d: Dict[str, Any], name: str = ""):
         from . import gigezen
 
         return gigezen.from_config_dict(d, name)
+    if str(d.get("architecture", "")).lower() == "seledra":
+        from . import seledra
+
+        return seledra.from_config_dict(d, name)
     mt = str(d.get("model_type", "")).lower()
     if mt == "gpt2":
         h = int(d["n_embd"])
@@ -114,7 +118,7 @@ def from_hf_dict(d: Dict[str, Any], name: str = ""):
                            int(d.get("max_position_embeddings", 4096)),
                            bool(d.get("tie_word_embeddings", False)), name,
                            d.get("bos_token_id"), eos)
-    raise ValueError(f"unsupported model_type {mt!r} (supported: gpt2, llama, mistral; architecture: Gigezen)")
+    raise ValueError(f"unsupported model_type {mt!r} (supported: gpt2, llama, mistral; architecture: Gigezen, Seledra)")
 
 
 def _llama(name, L, H, nh, nkv, I, V, theta=10000.0, maxpos=4096, scaling=None, eps=1e-5):
@@ -157,9 +161,9 @@ _ALIASES = {
 
 
 def _presets() -> Dict[str, Any]:
-    from . import gigezen
+    from . import gigezen, seledra
 
-    return {**PRESETS, **gigezen.PRESETS}
+    return {**PRESETS, **gigezen.PRESETS, **seledra.PRESETS}
 
 
 def resolve_config(model: str):

@@ -83,10 +83,19 @@ class GigezenConfig:
     tie_embeddings: bool = False
 
     is_llama = False
+    layer_list = True           # the runtime serves it with the layer-list span
+    parallel_block = True       # mixer and feed-forward read one norm and update the stream together
+    norm_gain_offset = NORM_GAIN_OFFSET
+    learned_positions = False
+    residual_mult = 1.0
+    cache_planes = 1
 
     @property
     def n_layers(self) -> int:
         return len(self.layers)
+
+    def state_elems(self, start: int = 0, end: Optional[int] = None) -> int:
+        return 0                # no recurrent layers: a sequence carries cache rows only
 
     # ---- cache layout: one plane of rows per cache-owning layer, all rows padded to the widest one
     def cache_layers(self, start: int = 0, end: Optional[int] = None) -> List[int]:

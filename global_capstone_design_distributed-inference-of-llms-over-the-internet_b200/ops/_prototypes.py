@@ -41,7 +41,7 @@ class AddNormArgs(C.Structure):
 
     _fields_ = [("x", vp), ("add_a", vp), ("add_b", vp), ("pair_y", vp), ("pair_w", vp), ("gain", vp), ("out", vp),
                 ("T", i32), ("width", i32), ("ldx", i32), ("lda", i32), ("ldb", i32), ("ldp", i32), ("top", i32),
-                ("ldo", i32), ("out_dtype", i32), ("eps", f32), ("gain_offset", f32), ("pdl", i32)]
+                ("ldo", i32), ("out_dtype", i32), ("eps", f32), ("gain_offset", f32), ("pdl", i32), ("add_scale", f32)]
 
 
 class SimtGemmArgs(C.Structure):
@@ -65,7 +65,38 @@ class LatentArgs(C.Structure):
                 ("pdl", i32), ("reserved", i32)]
 
 
+class SinkAttnArgs(C.Structure):
+    """Mirror of ``b200_sink_attn_args``."""
+
+    _fields_ = [("proj", vp), ("ldp", i32), ("q_off", i32), ("k_off", i32), ("v_off", i32), ("g_off", i32),
+                ("bias", vp), ("q_gain", vp), ("k_gain", vp), ("temp", vp), ("vmix", vp), ("v_first", vp),
+                ("ldvf", i32), ("vmix_mode", i32), ("k_cache", vp), ("v_cache", vp), ("kv_ptrs", vp), ("pos", vp),
+                ("kv_ptr_stride", i32), ("pos0", i32),
+                ("T", i32), ("heads", i32), ("kv_heads", i32), ("dim", i32), ("vdim", i32), ("row_elems", i32),
+                ("cache_dtype", i32), ("eps", f32), ("scale", f32), ("sink", f32), ("out", vp), ("ldo", i32),
+                ("out_dtype", i32), ("pdl", i32), ("reserved", i32)]
+
+
+class DeltaArgs(C.Structure):
+    """Mirror of ``b200_delta_args``."""
+
+    _fields_ = [("proj", vp), ("ldp", i32), ("c_off", i32), ("b_off", i32), ("a_off", i32), ("conv_w", vp), ("A_log", vp),
+                ("dt_bias", vp), ("work", vp), ("ldw", i32), ("state", vp), ("state_ptrs", vp), ("state_ptr_stride", i32),
+                ("reserved0", i32), ("state_off", i64), ("pos", vp), ("pos0", i32), ("n_seq", i32), ("seq_len", i32),
+                ("heads", i32), ("kv_heads", i32), ("dim", i32), ("vdim", i32), ("taps", i32), ("unit_eps", f32),
+                ("o", vp), ("ldo", i32), ("pdl", i32)]
+
+
 PROTOTYPES = [
+    ("b200_embed_pos_f32", [vp, vp, vp, i32, vp, i32, vp, i32, i32, i32, i32, i32, i32, vp], C.c_int),
+    ("b200_xielu", [vp, i32, vp, f32, f32, vp, i32, i32, i32, i32, i32, vp], C.c_int),
+    ("b200_sink_attn_append", [C.POINTER(SinkAttnArgs), vp], C.c_int),
+    ("b200_sink_attn", [C.POINTER(SinkAttnArgs), i32, vp, vp], C.c_int),
+    ("b200_sink_attn_prefill", [C.POINTER(SinkAttnArgs), vp], C.c_int),
+    ("b200_sink_attn_scratch_bytes", [i32, i32, i32, i32], i64),
+    ("b200_delta_prep", [C.POINTER(DeltaArgs), vp], C.c_int),
+    ("b200_delta_rule", [C.POINTER(DeltaArgs), vp], C.c_int),
+    ("b200_gated_head_norm", [vp, i32, vp, i32, vp, vp, i32, i32, i32, i32, i32, f32, i32, vp], C.c_int),
     ("b200_embed_f32", [vp, vp, i32, vp, i32, i32, i32, i32, i32, vp], C.c_int),
     ("b200_add_rms_norm", [C.POINTER(AddNormArgs), vp], C.c_int),
     ("b200_glu_clamp", [vp, vp, i32, vp, i32, i32, i32, i32, f32, f32, f32, i32, vp], C.c_int),

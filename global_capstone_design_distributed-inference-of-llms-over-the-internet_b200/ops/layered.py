@@ -1,5 +1,5 @@
 """Python front-ends of the kernels for layer-list designs with an fp32 residual stream
-(csrc/stream32.cu, csrc/gemm_simt.cu, csrc/latent_attention.cu, csrc/moe.cu)."""
+(csrc/stream32.cu, csrc/gemm_simt.cu, csrc/latent_attention.cu, csrc/moe.cu, csrc/sink_attention.cu, csrc/delta_rule.cu)."""
 from __future__ import annotations
 
 import ctypes
@@ -8,7 +8,7 @@ from typing import Optional
 import torch
 
 from . import native
-from ._prototypes import AddNormArgs, LatentArgs, SimtGemmArgs
+from ._prototypes import AddNormArgs, DeltaArgs, LatentArgs, SimtGemmArgs, SinkAttnArgs
 
 F16, BF16, F32 = 0, 1, 2
 
@@ -40,8 +40,9 @@ def embed_f32(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor, pdl: bo
 def add_rms_norm(x: torch.Tensor, gain: Optional[torch.Tensor], out: Optional[torch.Tensor], eps: float,
                  gain_offset: float = 0.0, add_a: Optional[torch.Tensor] = None, add_b: Optional[torch.Tensor] = None,
                  pair_y: Optional[torch.Tensor] = None, pair_w: Optional[torch.Tensor] = None, top: int = 0,
-                 pdl: bool = False) -> None:
-    """x (fp32 [T, W], updated in place) += add_a + add_b + sum_k pair_w * pair_y;  out = rms_norm(x) * (offset + gain)."""
+                 add_scale: float = 1.0, pdl: bool = False) -> None:
+    """x (fp32 [T, W], updated in place) += add_scale * (add_a + add_b + sum_k pair_w * pair_y);
+    out = rms_norm(x) * (offset + gain)."""
     assert x.dtype == torch.float32 and x.stride(1) == 1
     a = AddNormArgs()
     a.x, a.add_a, a.add_b, a.pair_y, a.pair_w, a.gain, a.out = _p(x), _p(add_a), _p(add_b), _p(pair_y), _p(pair_w), _p(gain), _p(out)
@@ -52,7 +53,7 @@ def add_rms_norm(x: torch.Tensor, gain: Optional[torch.Tensor], out: Optional[to
     a.top = top
     a.ldo = out.stride(0) if out is not None else 0
     a.out_dtype = code(out.dtype) if out is not None else F32
-    a.eps, a.gain_offset, a.pdl = eps, gain_offset, 1 if pdl else 0
+    a.eps, a.gain_offset, a.pdl, a.add_scale = eps, gain_offset, 1 if pdl else 0, add_scale
     for t in (add_a, add_b, pair_y, pair_w, gain):
         assert t is None or t.dtype == torch.float32
     native.check(native.lib().b200_add_rms_norm(ctypes.byref(a), _s()), "b200_add_rms_norm")
@@ -159,3 +160,111 @@ def latent_attn_prefill(proj: torch.Tensor, q_off: int, kvx: torch.Tensor, v_off
         proj.data_ptr(), proj.stride(0), q_off, kvx.data_ptr(), kvx.stride(0), v_off, cache.data_ptr(), cache.stride(0),
         kv_rank, out.data_ptr(), out.stride(0), T, heads, dim, rot, vdim, pos0, s0, window, scale, code(out.dtype),
         1 if pdl else 0, _s()), "b200_latent_attn_prefill")
+
+
+# ---------------------------------------------------------------- learned positions, piecewise activation
+def embed_pos_f32(ids: torch.Tensor, table: torch.Tensor, pos_table: torch.Tensor, out: torch.Tensor,
+                  pos: Optional[torch.Tensor] = None, pos0: int = 0, pdl: bool = False) -> torch.Tensor:
+    """out[t] = table[ids[t]] + pos_table[p_t] in fp32; p_t = pos[t] (int32 device tensor) or pos0 + t."""
+    assert ids.dtype == torch.int64 and out.dtype == torch.float32 and table.is_contiguous() and pos_table.is_contiguous()
+    assert table.dtype == pos_table.dtype and table.shape[1] == pos_table.shape[1]
+    native.check(native.lib().b200_embed_pos_f32(ids.data_ptr(), table.data_ptr(), pos_table.data_ptr(), code(table.dtype),
+                                                _p(pos), pos0, out.data_ptr(), ids.shape[0], table.shape[1], out.stride(0),
+                                                table.shape[0], pos_table.shape[0], 1 if pdl else 0, _s()), "b200_embed_pos_f32")
+    return out
+
+
+def xielu(z: torch.Tensor, params: torch.Tensor, act: torch.Tensor, lin: float = 0.5, neg_base: float = 0.5,
+          pdl: bool = False) -> None:
+    """z: fp32 [T, ff] view; params: fp32 [2] on the device; act: [T, >= ff]."""
+    assert z.dtype == torch.float32 and params.dtype == torch.float32 and z.stride(1) == 1
+    T, ff = z.shape
+    native.check(native.lib().b200_xielu(z.data_ptr(), z.stride(0), params.data_ptr(), lin, neg_base, act.data_ptr(),
+                                        act.stride(0), code(act.dtype), T, ff, 1 if pdl else 0, _s()), "b200_xielu")
+
+
+def gated_head_norm(o: torch.Tensor, gate: torch.Tensor, gain: torch.Tensor, out: torch.Tensor, heads: int, vdim: int,
+                    eps: float, pdl: bool = False) -> None:
+    """out[t, h] = rms_norm(o[t, h]) * gain * silu(gate[t, h]); o / gate: fp32 [T, >= heads * vdim] views."""
+    assert o.dtype == gate.dtype == gain.dtype == torch.float32
+    native.check(native.lib().b200_gated_head_norm(o.data_ptr(), o.stride(0), gate.data_ptr(), gate.stride(0), gain.data_ptr(),
+                                                  out.data_ptr(), out.stride(0), code(out.dtype), o.shape[0], heads, vdim, eps,
+                                                  1 if pdl else 0, _s()), "b200_gated_head_norm")
+
+
+# ---------------------------------------------------------------- attention with a sink
+def sink_attn_args(proj: torch.Tensor, *, q_off: int, k_off: int, v_off: int, g_off: int, heads: int, kv_heads: int, dim: int,
+                   vdim: int, row_elems: int, cache_dtype: torch.dtype, eps: float, scale: float, sink: float, T: int,
+                   bias: Optional[torch.Tensor] = None, q_gain: Optional[torch.Tensor] = None,
+                   k_gain: Optional[torch.Tensor] = None, temp: Optional[torch.Tensor] = None,
+                   vmix: Optional[torch.Tensor] = None, v_first: Optional[torch.Tensor] = None, vmix_mode: int = 0,
+                   k_cache: Optional[torch.Tensor] = None, v_cache: Optional[torch.Tensor] = None, pos0: int = 0,
+                   kv_ptrs: Optional[torch.Tensor] = None, kv_ptr_stride: int = 0, pos: Optional[torch.Tensor] = None,
+                   out: Optional[torch.Tensor] = None, pdl: bool = False) -> SinkAttnArgs:
+    assert proj.dtype == torch.float32
+    for t in (bias, q_gain, k_gain, temp, vmix, v_first):
+        assert t is None or t.dtype == torch.float32
+    a = SinkAttnArgs()
+    a.proj, a.ldp, a.q_off, a.k_off, a.v_off, a.g_off = proj.data_ptr(), proj.stride(0), q_off, k_off, v_off, g_off
+    a.bias, a.q_gain, a.k_gain, a.temp, a.vmix, a.v_first = _p(bias), _p(q_gain), _p(k_gain), _p(temp), _p(vmix), _p(v_first)
+    a.ldvf = v_first.stride(0) if v_first is not None else 0
+    a.vmix_mode = vmix_mode
+    a.k_cache, a.v_cache, a.kv_ptrs, a.pos = _p(k_cache), _p(v_cache), _p(kv_ptrs), _p(pos)
+    a.kv_ptr_stride, a.pos0 = kv_ptr_stride, pos0
+    a.T, a.heads, a.kv_heads, a.dim, a.vdim, a.row_elems = T, heads, kv_heads, dim, vdim, row_elems
+    a.cache_dtype, a.eps, a.scale, a.sink = code(cache_dtype), eps, scale, sink
+    a.out = _p(out)
+    a.ldo = out.stride(0) if out is not None else 0
+    a.out_dtype = code(out.dtype) if out is not None else F32
+    a.pdl = 1 if pdl else 0
+    return a
+
+
+def sink_attn_append(a: SinkAttnArgs) -> None:
+    native.check(native.lib().b200_sink_attn_append(ctypes.byref(a), _s()), "b200_sink_attn_append")
+
+
+def sink_attn(a: SinkAttnArgs, splits: int = 1, scratch: Optional[torch.Tensor] = None) -> None:
+    """splits > 1: ``scratch`` is an fp32 tensor of at least T * heads * splits * (vdim + 2) elements."""
+    if splits > 1:
+        assert scratch is not None and scratch.dtype == torch.float32 and \
+            scratch.numel() >= a.T * a.heads * splits * (a.vdim + 2)
+    native.check(native.lib().b200_sink_attn(ctypes.byref(a), splits, _p(scratch) if splits > 1 else None, _s()), "b200_sink_attn")
+
+
+def sink_attn_prefill_fits(dim: int, vdim: int) -> bool:
+    """Can the tensor-core kernel take heads of these sizes?"""
+    return hasattr(native.lib(), "b200_sink_attn_prefill") and dim % 16 == 0 and vdim % 16 == 0 and dim <= 128 and vdim <= 128
+
+
+def sink_attn_prefill(a: SinkAttnArgs) -> None:
+    native.check(native.lib().b200_sink_attn_prefill(ctypes.byref(a), _s()), "b200_sink_attn_prefill")
+
+
+# ---------------------------------------------------------------- gated delta rule
+def delta_args(proj: torch.Tensor, *, c_off: int, b_off: int, a_off: int, conv_w: torch.Tensor, A_log: torch.Tensor,
+               dt_bias: torch.Tensor, work: torch.Tensor, o: torch.Tensor, heads: int, kv_heads: int, dim: int, vdim: int,
+               taps: int, unit_eps: float, n_seq: int, seq_len: int, state: Optional[torch.Tensor] = None,
+               state_ptrs: Optional[torch.Tensor] = None, state_ptr_stride: int = 0, state_off: int = 0,
+               pos: Optional[torch.Tensor] = None, pos0: int = 0, pdl: bool = False) -> DeltaArgs:
+    for t in (proj, conv_w, A_log, dt_bias, work, o, state):
+        assert t is None or t.dtype == torch.float32
+    assert work.shape[1] >= 2 * kv_heads * dim + heads * vdim + 2 * heads
+    a = DeltaArgs()
+    a.proj, a.ldp, a.c_off, a.b_off, a.a_off = proj.data_ptr(), proj.stride(0), c_off, b_off, a_off
+    a.conv_w, a.A_log, a.dt_bias = conv_w.data_ptr(), A_log.data_ptr(), dt_bias.data_ptr()
+    a.work, a.ldw = work.data_ptr(), work.stride(0)
+    a.state, a.state_ptrs, a.state_ptr_stride, a.state_off = _p(state), _p(state_ptrs), state_ptr_stride, state_off
+    a.pos, a.pos0 = _p(pos), pos0
+    a.n_seq, a.seq_len, a.heads, a.kv_heads, a.dim, a.vdim, a.taps = n_seq, seq_len, heads, kv_heads, dim, vdim, taps
+    a.unit_eps = unit_eps
+    a.o, a.ldo, a.pdl = o.data_ptr(), o.stride(0), 1 if pdl else 0
+    return a
+
+
+def delta_prep(a: DeltaArgs) -> None:
+    native.check(native.lib().b200_delta_prep(ctypes.byref(a), _s()), "b200_delta_prep")
+
+
+def delta_rule(a: DeltaArgs) -> None:
+    native.check(native.lib().b200_delta_rule(ctypes.byref(a), _s()), "b200_delta_rule")

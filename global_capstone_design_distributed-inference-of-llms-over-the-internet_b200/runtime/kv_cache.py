@@ -25,12 +25,14 @@ from .memory_cache import AllocationFailed, MemoryCache, TensorDescriptor  # noq
 @dataclass
 class SessionKV:
     session_id: str
-    data: torch.Tensor            # [n_layers, planes, n_kv, max_len, head_dim] (planes: K and V, or 1 for latent rows)
+    data: torch.Tensor            # [n_layers, planes, n_kv, max_len, head_dim] (planes: K and V, or 1 for latent rows;
+                                  #  layer-list designs: n_layers = cache-owning layers, n_kv = 1, head_dim = padded row)
     max_len: int
     length: int = 0               # tokens cached so far
     last_used: float = field(default_factory=time.monotonic)
     limit: Optional[int] = None   # request-level max_length (<= max_len), enforced by the handler
     release: Optional[Callable[[], None]] = None   # returns the bytes to the manager's MemoryCache
+    state: Optional[torch.Tensor] = None           # fp32 [state_elems]: what recurrent layers carry (None: no such layers)
 
     @property
     def n_layers(self) -> int:
@@ -47,9 +49,17 @@ class SessionKV:
         shared by all heads; a slot is a cache-OWNING layer, layers that read another layer's cache have none)."""
         return self.data[slot, 0, 0]
 
+    def plane(self, slot: int, which: int) -> torch.Tensor:
+        """[max_len, row] rows of plane ``which`` (0 = keys, 1 = values) of cache slot ``slot`` in a layout that keeps
+        all key (value) heads of a token in one row."""
+        return self.data[slot, which, 0]
+
     def rollback(self, position: int) -> None:
         if not 0 <= position <= self.length:
             raise ValueError(f"cannot roll session back to {position} (length {self.length})")
+        if self.state is not None and position not in (0, self.length):
+            # (position 0 is fine: a recurrent layer reads no state at a sequence's first token)
+            raise ValueError("a session with recurrent state can only be rolled back to its start")
         self.length = position
 
     def touch(self) -> None:
@@ -59,8 +69,11 @@ class SessionKV:
 class KVCacheManager:
     def __init__(self, n_layers: int, n_kv_heads: int, head_dim: int, dtype: torch.dtype, device,
                  max_tokens: Optional[int] = None, default_max_length: int = 2048, session_ttl: float = 600.0,
-                 alloc_timeout: float = 0.0, planes: int = 2):
+                 alloc_timeout: float = 0.0, planes: int = 2, state_elems: int = 0, max_sessions: int = 64):
         self.n_layers, self.n_kv, self.head_dim, self.planes = n_layers, n_kv_heads, head_dim, int(planes)
+        # fp32 numbers per session that do not grow with its length (recurrent layers); the byte budget sets aside
+        # room for ``max_sessions`` of them beside the per-token bytes
+        self.state_elems, self.max_sessions = int(state_elems), int(max_sessions)
         self.dtype, self.device = dtype, torch.device(device)
         self.max_tokens = max_tokens              # None = unlimited
         self.default_max_length = default_max_length
@@ -69,14 +82,16 @@ class KVCacheManager:
         self.sessions: Dict[str, SessionKV] = {}
         self._lock = threading.Lock()
         # every session buffer is carved from this byte budget; waiters are woken when a session closes
-        self.cache = MemoryCache(None if max_tokens is None else max_tokens * self.bytes_per_token(), alloc_timeout)
+        self.cache = MemoryCache(None if max_tokens is None else max_tokens * self.bytes_per_token() +
+                                 self.max_sessions * 4 * self.state_elems, alloc_timeout)
 
     @classmethod
     def for_span(cls, cfg, start: int, end: int, dtype: torch.dtype, device, tp: int = 1, **kw) -> "KVCacheManager":
         """The manager whose sessions fit blocks [start, end) of ``cfg``: K and V planes per block and kv head for the
         uniform families, one plane of latent rows per cache-owning layer for layer-list designs."""
-        if getattr(cfg, "family", "") == "gigezen":
-            return cls(max(1, len(cfg.cache_layers(start, end))), 1, cfg.cache_row(start, end), dtype, device, planes=1, **kw)
+        if getattr(cfg, "layer_list", False):
+            return cls(max(1, len(cfg.cache_layers(start, end))), 1, cfg.cache_row(start, end), dtype, device,
+                       planes=cfg.cache_planes, state_elems=cfg.state_elems(start, end), **kw)
         return cls(end - start, cfg.n_kv_heads // tp, cfg.head_dim, dtype, device, **kw)
 
     # ---- accounting
@@ -122,15 +137,18 @@ class KVCacheManager:
             self._drop(session_id)
             if self.max_tokens is not None and self.tokens_used + max_length > self.max_tokens:
                 self._evict_lru_until(max_length)
-        desc = TensorDescriptor((self.n_layers, self.planes, self.n_kv, max_length, self.head_dim), self.dtype, self.device)
+        desc = [TensorDescriptor((self.n_layers, self.planes, self.n_kv, max_length, self.head_dim), self.dtype, self.device)]
+        if self.state_elems:
+            desc.append(TensorDescriptor((self.state_elems,), torch.float32, self.device))
         stack = contextlib.ExitStack()
         try:
-            handles = stack.enter_context(self.cache.allocate_cache(desc, timeout=timeout))   # may block (no lock held)
+            handles = stack.enter_context(self.cache.allocate_cache(*desc, timeout=timeout))   # may block (no lock held)
         except AllocationFailed as e:
             raise AllocationFailed(f"KV budget exhausted: need {max_length} tokens, {self.tokens_left} left of "
                                    f"{self.max_tokens} ({e})") from None
-        data = self.cache.use_cache(*handles)[0]
-        s = SessionKV(session_id, data, max_length, release=stack.close)
+        tensors = self.cache.use_cache(*handles)
+        s = SessionKV(session_id, tensors[0], max_length, release=stack.close,
+                      state=tensors[1] if self.state_elems else None)
         with self._lock:
             self._drop(session_id)          # a concurrent allocate for the same id loses
             self.sessions[session_id] = s
@@ -146,14 +164,17 @@ class KVCacheManager:
         if len(src_idx) != len(sess) or any(not 0 <= h < len(sess) for h in src_idx):
             raise ValueError("hypo_ids must index into session_ids")
         need = {h for i, h in enumerate(src_idx) if h != i}
-        snap = {h: (sess[h].data[:, :, :, : sess[h].length].clone(), sess[h].length) for h in need}
+        snap = {h: (sess[h].data[:, :, :, : sess[h].length].clone(), sess[h].length,
+                    None if sess[h].state is None else sess[h].state.clone()) for h in need}
         for i, h in enumerate(src_idx):
             if h == i:
                 continue
-            data, length = snap[h]
+            data, length, state = snap[h]
             if length > sess[i].max_len:
                 raise ValueError("destination session is too small for the source hypothesis")
             sess[i].data[:, :, :, :length].copy_(data)
+            if state is not None:
+                sess[i].state.copy_(state)
             sess[i].length = length
             sess[i].touch()
 

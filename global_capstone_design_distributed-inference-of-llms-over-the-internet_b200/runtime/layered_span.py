@@ -1,4 +1,4 @@
-"""B200 execution of a span of a layer-list design (first user: Gigezen) with an fp32 residual stream.
+"""B200 execution of a span of a layer-list design (Gigezen, Seledra) with an fp32 residual stream.
 
 ``LayeredSpan`` plugs into everything a :class:`NativeSpan` plugs into - sessions of the cache manager, the
 captured decode step with its staged positions / cache pointers, the device sampler, the pipeline engine and the
@@ -14,6 +14,19 @@ and the head.  Per layer (T tokens of any mix of sessions):
     y     = cat . [Wo | Wdown]^T                                     tcgen05 GEMM, fp32 out: mixer + dense ff in one
     experts (mixture layers): route, plan, grouped gate/up and down  b200_moe_* + b200_gemm_simt (grouped)
 
+A design whose layers update the stream in two steps (Seledra: ``x += m mixer(norm1 x)``, ``x += m ff(norm2 x)``) runs
+
+    hn    = rms_norm(x += m * previous sublayer's output) * g         b200_add_rms_norm
+    proj  = hn . [Wq | Wk | Wv | Wgate]^T  (attention)                tcgen05 GEMM, fp32 out (one launch)
+            hn . [Wq | Wk | Wv | Wbeta | Wdecay | Wgate]^T  (delta)
+    attention: norms, value blending, cache append                   b200_sink_attn_append
+               softmax with a sink over the cached rows, head gate    b200_sink_attn / b200_sink_attn_prefill
+    delta:     convolutions, unit q / k, beta, decay                  b200_delta_prep
+               the recurrence over the session's state                b200_delta_rule
+               gated RMS norm per head                                b200_gated_head_norm
+    y     = heads . Wo^T                                              tcgen05 GEMM, fp32 out
+    feed-forward: norm (as above), up GEMM, b200_xielu, down GEMM
+
 ``dtype=torch.float32`` runs the same step with every product in true fp32 (``b200_gemm_simt`` instead of the
 tensor-core GEMM) and an fp32 cache.
 """
@@ -25,6 +38,7 @@ from typing import Dict, List, Optional, Sequence
 import torch
 
 from ..models import gigezen as Z
+from ..models import seledra as SD
 from ..ops import elementwise as E
 from ..ops import gemm as G
 from ..ops import layered as L
@@ -60,7 +74,7 @@ class _Linear:
 class LayeredSpan(NativeSpan):
     hidden_dtype = torch.float32        # what enters and leaves the span between pipeline stages
 
-    def __init__(self, cfg: Z.GigezenConfig, weights: Dict[str, object], device, dtype: torch.dtype, *,
+    def __init__(self, cfg, weights: Dict[str, object], device, dtype: torch.dtype, *,
                  kv_capacity: int = 2048, max_batch: int = 8, max_chunk: int = 512, use_graphs: bool = True,
                  pdl: Optional[bool] = None, free_source_weights: bool = True, weight_format: str = "native",
                  head_rows: Optional[tuple] = None, attn_splits: int = 0, streamed_layers: int = 0):
@@ -87,11 +101,23 @@ class LayeredSpan(NativeSpan):
         slots = {a: s for s, a in enumerate(cfg.cache_layers(self.start, self.start + len(specs)))}
         self.n_slots = max(1, len(slots))
         self.row_elems = cfg.cache_row(self.start, self.start + len(specs))
+        self.cache_planes = cfg.cache_planes
+        # recurrent layers: a session carries fp32 state; its address travels in one more row of the pointer table
+        self.state_elems = cfg.state_elems(self.start, self.start + len(specs))
+        self.state_slot = self.n_slots if self.state_elems else None
+        state_off = cfg.state_offsets(self.start, self.start + len(specs)) if self.state_elems else {}
+        self.gain_offset = float(cfg.norm_gain_offset)
+        self.residual_mult = float(cfg.residual_mult)
         with torch.cuda.device(self.device):
             self.layers: List[dict] = []
             self._inv_freq: Dict[tuple, torch.Tensor] = {}
             for i, (S, Lw) in enumerate(zip(specs, weights["layers"])):   # type: ignore[arg-type]
                 m = S.mixer
+                if isinstance(m, (SD.SinkAttentionSpec, SD.DeltaRuleSpec)):
+                    self.layers.append(self._pack_two_step_layer(S, Lw, slots.get(self.start + i),
+                                                                 state_off.get(self.start + i, 0), self.start + i,
+                                                                 free_source_weights))
+                    continue
                 parts, P = [Lw["q_w"]], {"spec": S, "norm_w": Lw["norm1_w"], "q_off": 0, "kv_off": -1}
                 n = m.q_size
                 if m.owns_cache:
@@ -137,7 +163,7 @@ class LayeredSpan(NativeSpan):
                             (("e_gate", "e_up", "e_down") if "e_in" in P else ()):
                         Lw.pop(k, None)
             self.embed_w = weights.get("embed") if self.has_embed else None
-            self.pos_embed_w = None
+            self.pos_embed_w = weights.get("pos_embed") if self.has_embed else None
             self.head_lo, self.head_hi = 0, cfg.vocab
             if self.has_head:
                 self.final_norm_w = weights["final_norm_w"]
@@ -150,13 +176,21 @@ class LayeredSpan(NativeSpan):
             self.h_a = f32(Tm, W)
             self.h_b = self.h_a                                      # (one stream buffer: layers update it in place)
             self.hn = act(Tm, _pad64(W))
-            self.proj = f32(Tm, mx(lambda P: P["proj"].n))
-            self.qa = f32(Tm, mx(lambda P: P["spec"].mixer.heads * P["spec"].mixer.kv_rank))
+            self.proj = f32(Tm, mx(lambda P: max(P["proj"].n, P["up"].n if "up" in P else 0)))
+            latent = lambda P: isinstance(P["spec"].mixer, Z.LatentAttentionSpec)  # noqa: E731
+            self.qa = f32(Tm, mx(lambda P: P["spec"].mixer.heads * P["spec"].mixer.kv_rank if latent(P) else 1))
             self.ol = torch.zeros_like(self.qa)
-            self.cat = act(Tm, mx(lambda P: _pad64(P["out"].k)))
+            self.cat = act(Tm, mx(lambda P: _pad64(max(P["out"].k, P["down"].k if "down" in P else 0))))
             self.y = f32(Tm, W)
             self.attn_part = f32(MAX_DECODE_BATCH * ATTN_MAX_SPLITS *
-                                 mx(lambda P: P["spec"].mixer.heads * (P["spec"].mixer.kv_rank + 2)))
+                                 mx(lambda P: P["spec"].mixer.heads * ((P["spec"].mixer.kv_rank if latent(P) else
+                                                                        getattr(P["spec"].mixer, "vdim", 0)) + 2)))
+            deltas = [P["spec"].mixer for P in self.layers if isinstance(P["spec"].mixer, SD.DeltaRuleSpec)]
+            if deltas:     # what the recurrence reads (q | k | v | beta | decay) and its raw read-out, fp32
+                self.delta_work = f32(Tm, max(d.conv_channels + 2 * d.heads for d in deltas))
+                self.delta_o = f32(Tm, max(d.v_size for d in deltas))
+            vm = [P["spec"].mixer for P in self.layers if getattr(P["spec"].mixer, "v_mix", False)]
+            self.v_first = f32(Tm, max(v.v_size for v in vm)) if vm else None
             moe = [P["spec"].mlp for P in self.layers if isinstance(P["spec"].mlp, Z.MoESpec)]
             if moe:
                 top, ne, ffe = max(e.top for e in moe), max(e.experts for e in moe), max(e.ff for e in moe)
@@ -172,9 +206,9 @@ class LayeredSpan(NativeSpan):
             self.ids_in = torch.zeros(Tm, dtype=torch.int64, device=self.device)
             # expanded keys / values of the rows a chunk can see (16-bit modes, allocated with the first such chunk)
             self.kvx = None
-            self.kvx_rows = Tm + min(mx(lambda P: P["spec"].mixer.window - 1), self.kv_capacity)
+            self.kvx_rows = Tm + min(mx(lambda P: getattr(P["spec"].mixer, "window", 1) - 1), self.kv_capacity)
             self.ws = None if ex else G.GemmWorkspace.create(self.device, max(Tm, min(self.kvx_rows, 256)))
-            self._make_stage_buffers(self.n_slots)
+            self._make_stage_buffers(self._cache_slots())
             self.sampler = None
             self._seq_host = 0
             self.chain_tokens = 0
@@ -192,7 +226,41 @@ class LayeredSpan(NativeSpan):
 
     # ------------------------------------------------------------------ framework hooks
     def _cache_slots(self) -> int:
-        return self.n_slots
+        return self.n_slots + (1 if self.state_elems else 0)
+
+    def _ptr_column(self, kv: SessionKV, nl: int) -> torch.Tensor:
+        col = super()._ptr_column(kv, nl)
+        if self.state_elems:          # last row: where the session's recurrent state lives
+            if kv.state is None or kv.state.numel() < self.state_elems:
+                raise ValueError(f"session {kv.session_id} carries no state for this span's recurrent layers")
+            col[self.state_slot, 0] = kv.state.data_ptr()
+            col[self.state_slot, 1] = 0
+        return col
+
+    def _pack_two_step_layer(self, S, Lw: dict, slot: Optional[int], state_off: int, index: int, free: bool) -> dict:
+        """Weights of a layer that updates the stream in two steps (mixer, then feed-forward), in the span's mode."""
+        ex, m = self.exact, S.mixer
+        P = {"spec": S, "norm_w": Lw["norm1_w"], "slot": slot, "state_off": state_off, "hv": m.heads * m.vdim}
+        if isinstance(m, SD.SinkAttentionSpec):
+            P["proj"] = _Linear(torch.cat([Lw["q_w"], Lw["k_w"], Lw["v_w"], Lw["g_w"]], 0), ex)
+            P["q_off"], P["k_off"], P["v_off"], P["g_off"] = 0, m.q_size, m.q_size + m.k_size, m.q_size + m.k_size + m.v_size
+            for k in ("qkv_b", "q_norm_w", "k_norm_w", "temp", "vmix"):
+                P[k] = Lw[k]
+            P["vmix_mode"] = 0 if not m.v_mix else (1 if index == self.cfg.first_vmix_layer() else 2)
+        else:
+            P["proj"] = _Linear(torch.cat([Lw["q_w"], Lw["k_w"], Lw["v_w"], Lw["b_w"], Lw["a_w"], Lw["g_w"]], 0), ex)
+            P["c_off"], P["b_off"], P["a_off"] = 0, m.conv_channels, m.conv_channels + m.heads
+            P["g_off"] = m.conv_channels + 2 * m.heads
+            for k in ("conv_w", "A_log", "dt_bias", "o_norm_w"):
+                P[k] = Lw[k]
+        P["out"] = _Linear(Lw["o_w"], ex)
+        if S.mlp is not None:
+            P["norm2_w"], P["act"] = Lw["norm2_w"], Lw["act"]
+            P["up"], P["down"] = _Linear(Lw["up_w"], ex), _Linear(Lw["down_w"], ex)
+        if free:
+            for k in ("q_w", "k_w", "v_w", "g_w", "b_w", "a_w", "o_w", "up_w", "down_w"):
+                Lw.pop(k, None)
+        return P
 
     def subspan(self, a: int, b: int):
         if (a, b) == (0, len(self.layers)):
@@ -202,7 +270,8 @@ class LayeredSpan(NativeSpan):
     def weight_bytes(self) -> int:
         n = 0
         for P in self.layers:
-            n += P["proj"].nbytes + P["out"].nbytes + sum(P[k].numel() * P[k].element_size() for k in ("ukT", "uv"))
+            n += P["proj"].nbytes + P["out"].nbytes + sum(P[k].numel() * P[k].element_size() for k in ("ukT", "uv") if k in P)
+            n += sum(P[k].nbytes for k in ("up", "down") if k in P)
             if "e_gate" in P:
                 n += sum(P[k].numel() * P[k].element_size() for k in ("e_gate", "e_up", "e_down"))
             if "e_in" in P:
@@ -224,7 +293,11 @@ class LayeredSpan(NativeSpan):
 
     def _embed(self, T: int, pos0: int, use_pos_buffer: bool) -> torch.Tensor:
         h = self.h_a[:T]
-        L.embed_f32(self.ids_in[:T], self.embed_w, h, pdl=self.pdl)
+        if self.pos_embed_w is not None:      # learned positions, added in fp32
+            L.embed_pos_f32(self.ids_in[:T], self.embed_w, self.pos_embed_w, h, pos=self.pos[:T] if use_pos_buffer else None,
+                            pos0=pos0, pdl=self.pdl)
+        else:
+            L.embed_f32(self.ids_in[:T], self.embed_w, h, pdl=self.pdl)
         self._count()
         return h
 
@@ -233,7 +306,7 @@ class LayeredSpan(NativeSpan):
         pend, self._pending = self._pending or {}, None
         if not pend and out is None:
             return
-        L.add_rms_norm(x, gain, out, self.cfg.norm_eps, Z.NORM_GAIN_OFFSET, pdl=self.pdl, **pend)
+        L.add_rms_norm(x, gain, out, self.cfg.norm_eps, self.gain_offset, add_scale=self.residual_mult, pdl=self.pdl, **pend)
         self._count()
 
     def _attn_splits(self, T: int, m) -> tuple:
@@ -249,6 +322,8 @@ class LayeredSpan(NativeSpan):
     def _layer(self, T: int, x: torch.Tensor, P: dict, where: dict) -> None:
         S, pdl = P["spec"], self.pdl
         m = S.mixer
+        if not isinstance(m, Z.LatentAttentionSpec):
+            return self._layer_two_step(T, x, P, where)
         W = self.cfg.hidden
         hn, proj, cat = self.hn[:T], self.proj[:T], self.cat[:T]
         self._flush(x, P["norm_w"], hn[:, :W])
@@ -277,6 +352,71 @@ class LayeredSpan(NativeSpan):
         self._pending = dict(add_a=self.y[:T])
         if isinstance(S.mlp, Z.MoESpec):
             self._experts(T, P, hn, proj)
+
+    # ------------------------------------------------------------------ layers of two residual steps
+    def _layer_two_step(self, T: int, x: torch.Tensor, P: dict, where: dict) -> None:
+        S, pdl = P["spec"], self.pdl
+        W = self.cfg.hidden
+        hn, proj, cat = self.hn[:T], self.proj[:T], self.cat[:T]
+        self._flush(x, P["norm_w"], hn[:, :W])
+        self._linear(hn, P["proj"], proj)
+        if isinstance(S.mixer, SD.SinkAttentionSpec):
+            self._mixer_sink_attention(T, P, where, proj, cat)
+        else:
+            self._mixer_delta(T, P, where, proj, cat)
+        self._linear(cat, P["out"], self.y[:T])
+        self._pending = dict(add_a=self.y[:T])
+        if S.mlp is not None:
+            ff = S.mlp.ff
+            self._flush(x, P["norm2_w"], hn[:, :W])
+            self._linear(hn, P["up"], proj)
+            L.xielu(proj[:, :ff], P["act"], cat, lin=SD.XIELU_LINEAR, neg_base=SD.XIELU_LINEAR, pdl=pdl)
+            self._count()
+            self._linear(cat, P["down"], self.y[:T])
+            self._pending = dict(add_a=self.y[:T])
+
+    def _sink_splits(self, T: int, m) -> tuple:
+        """Decode-size steps divide every token's keys over several blocks; the split depends on the step's size and
+        the sessions' capacity only, so a captured step keeps it."""
+        if T > MAX_DECODE_BATCH:
+            return 1, None
+        splits = max(1, min(ATTN_MAX_SPLITS, self.kv_capacity // 128, (4 * 148) // (T * m.heads)))
+        return (splits, self.attn_part) if splits > 1 else (1, None)
+
+    def _mixer_sink_attention(self, T: int, P: dict, where: dict, proj: torch.Tensor, cat: torch.Tensor) -> None:
+        m = P["spec"].mixer
+        kw = dict(q_off=P["q_off"], k_off=P["k_off"], v_off=P["v_off"], g_off=P["g_off"], heads=m.heads, kv_heads=m.kv_heads,
+                  dim=m.dim, vdim=m.vdim, row_elems=self.row_elems, cache_dtype=self.dtype, eps=self.cfg.norm_eps,
+                  scale=m.scale, sink=m.sink, T=T, bias=P["qkv_b"], q_gain=P["q_norm_w"], k_gain=P["k_norm_w"], temp=P["temp"],
+                  vmix=P["vmix"], v_first=self.v_first, vmix_mode=P["vmix_mode"], out=cat, pdl=self.pdl)
+        if "kv" in where:      # one session: its planes, consecutive positions
+            kv = where["kv"]
+            kw.update(k_cache=kv.plane(P["slot"], 0), v_cache=kv.plane(P["slot"], 1), pos0=where["pos0"])
+        else:                  # a batch of sessions: staged pointer table and positions
+            kw.update(kv_ptrs=self.kv_ptrs[P["slot"]], kv_ptr_stride=2, pos=self.pos)
+        a = L.sink_attn_args(proj, **kw)
+        L.sink_attn_append(a)
+        if "kv" in where and not self.exact and T >= TC_ATTN_MIN_TOKENS and L.sink_attn_prefill_fits(m.dim, m.vdim):
+            L.sink_attn_prefill(a)
+        else:
+            L.sink_attn(a, *self._sink_splits(T, m))
+        self._count(2)
+
+    def _mixer_delta(self, T: int, P: dict, where: dict, proj: torch.Tensor, cat: torch.Tensor) -> None:
+        m = P["spec"].mixer
+        kw = dict(c_off=P["c_off"], b_off=P["b_off"], a_off=P["a_off"], conv_w=P["conv_w"], A_log=P["A_log"],
+                  dt_bias=P["dt_bias"], work=self.delta_work[:T], o=self.delta_o[:T], heads=m.heads, kv_heads=m.kv_heads,
+                  dim=m.dim, vdim=m.vdim, taps=m.conv, unit_eps=m.unit_eps, state_off=P["state_off"], pdl=self.pdl)
+        if "kv" in where:      # a chunk of one session: its tokens in order
+            kw.update(state=where["kv"].state, pos0=where["pos0"], n_seq=1, seq_len=T)
+        else:                  # a batch of sessions, one token each
+            kw.update(state_ptrs=self.kv_ptrs[self.state_slot], state_ptr_stride=2, pos=self.pos, n_seq=T, seq_len=1)
+        a = L.delta_args(proj, **kw)
+        L.delta_prep(a)
+        L.delta_rule(a)
+        L.gated_head_norm(self.delta_o[:T], proj[:, P["g_off"]:], P["o_norm_w"], cat, m.heads, m.vdim, self.cfg.norm_eps,
+                          pdl=self.pdl)
+        self._count(3)
 
     def _attn_tensor_core(self, T: int, P: dict, where: dict, proj: torch.Tensor, cat: torch.Tensor) -> None:
         """A chunk of one session: expand the visible latents with one tensor-core GEMM, then flash attention on them."""
@@ -356,7 +496,7 @@ class LayeredSpan(NativeSpan):
         assert B <= self.head_rows_max and init_pair is None and out_pair is None
         hn = self.hn[:B]
         if not (getattr(self, "_normed", False) and h_rows.data_ptr() == self.h_a.data_ptr()):
-            L.add_rms_norm(h_rows, self.final_norm_w, hn[:, :W], self.cfg.norm_eps, Z.NORM_GAIN_OFFSET, pdl=self.pdl)
+            L.add_rms_norm(h_rows, self.final_norm_w, hn[:, :W], self.cfg.norm_eps, self.gain_offset, pdl=self.pdl)
             self._count()
         self._normed = False
         logits = self.logits[:B]
@@ -384,9 +524,11 @@ class LayeredSpan(NativeSpan):
         T = ids.shape[0] if h_in is None else h_in.shape[0]
         if pos0 + T > kv.max_len:
             raise ValueError(f"session {kv.session_id}: {pos0}+{T} tokens exceed max_length {kv.max_len}")
-        if kv.max_len != self.kv_capacity or kv.data.shape[0] != self.n_slots or kv.data.shape[-1] != self.row_elems:
+        if kv.max_len != self.kv_capacity or kv.data.shape[0] != self.n_slots or kv.data.shape[-1] != self.row_elems or \
+                kv.data.shape[1] != self.cache_planes or (self.state_elems and (kv.state is None or kv.state.numel() < self.state_elems)):
             raise ValueError(f"session cache {tuple(kv.data.shape)} does not fit this span "
-                             f"({self.n_slots} slots x {self.kv_capacity} rows x {self.row_elems})")
+                             f"({self.n_slots} slots x {self.cache_planes} planes x {self.kv_capacity} rows x {self.row_elems}, "
+                             f"{self.state_elems} state elements)")
         W = self.cfg.hidden
         want = None if logits_at is None else sorted(set(int(i) for i in logits_at))
         out = None if self.has_head else torch.empty(T, W, dtype=torch.float32, device=self.device)
@@ -440,7 +582,7 @@ class LayeredSpan(NativeSpan):
 
 def make_span(cfg, weights, device, dtype, **kw):
     """The span class of a configuration's family (the one place the runtime chooses between them)."""
-    if getattr(cfg, "family", "") == "gigezen":
+    if getattr(cfg, "layer_list", False):
         return LayeredSpan(cfg, weights, device, dtype, **kw)
     return NativeSpan(cfg, weights, device, dtype, **kw)
 
@@ -449,6 +591,6 @@ def span_runs_natively(cfg, device, dtype) -> bool:
     """Does the family have a CUDA span for this element type?"""
     if torch.device(device).type != "cuda":
         return False
-    if getattr(cfg, "family", "") == "gigezen":
+    if getattr(cfg, "layer_list", False):
         return dtype in (torch.float16, torch.bfloat16, torch.float32)
     return dtype in (torch.float16, torch.bfloat16)

@@ -527,11 +527,7 @@ class NativeSpan:
                         raise ValueError(f"session capacity {kv.max_len} != engine kv_capacity {self.kv_capacity}")
                     col = getattr(kv, "_ptr_col", None)
                     if col is None or col.shape[0] != nl or int(col[0, 0]) != kv.data.data_ptr():
-                        base = kv.data.data_ptr()
-                        per_layer = kv.data.stride(0) * kv.data.element_size()
-                        half = kv.data.stride(1) * kv.data.element_size()
-                        k_ptr = base + torch.arange(max(nl, 1), dtype=torch.int64) * per_layer
-                        col = kv._ptr_col = torch.stack([k_ptr, k_ptr + half], 1)
+                        col = kv._ptr_col = self._ptr_column(kv, max(nl, 1))
                     if nl:
                         tab[:, b] = col
                 if len(self._ptr_tables) > 256:
@@ -549,6 +545,14 @@ class NativeSpan:
         host[self.max_batch] = self._seq_host
         self._stage_dev[:n_copy].copy_(host[:n_copy], non_blocking=True)
         ev.record(torch.cuda.current_stream(self.device))
+
+    def _ptr_column(self, kv: SessionKV, nl: int) -> torch.Tensor:
+        """[nl, 2] int64: the addresses of a session's planes, one row per cache slot (keys, values)."""
+        base = kv.data.data_ptr()
+        per_layer = kv.data.stride(0) * kv.data.element_size()
+        half = kv.data.stride(1) * kv.data.element_size()
+        k_ptr = base + torch.arange(nl, dtype=torch.int64) * per_layer
+        return torch.stack([k_ptr, k_ptr + half], 1)
 
     def prestage(self, kvs: Sequence[SessionKV]) -> None:
         """Queue the NEXT step's positions / cache pointers behind the step that was just launched, so a host loop

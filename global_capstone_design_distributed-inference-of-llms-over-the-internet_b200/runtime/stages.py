@@ -49,7 +49,7 @@ class StageWeights:
 
 def load_stage_weights(model_name: str, device, role: str, *, start: int = 0, end: Optional[int] = None,
                        dtype: torch.dtype = torch.float16, use_cpu_offload: bool = False, seed: int = 0,
-                       families=("llama", "gpt2", "gigezen")) -> StageWeights:
+                       families=("llama", "gpt2", "gigezen", "seledra")) -> StageWeights:
     cfg = resolve_config(model_name)
     if cfg.family not in families:
         raise ValueError(f"{model_name}: family {cfg.family!r} is not handled by this module ({families})")

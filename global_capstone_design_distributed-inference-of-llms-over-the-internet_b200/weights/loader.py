@@ -61,6 +61,10 @@ def hf_shapes(cfg: ModelConfig) -> Dict[str, tuple]:
         from ..models import gigezen
 
         return gigezen.tensor_shapes(cfg)
+    if cfg.family == "seledra":
+        from ..models import seledra
+
+        return seledra.tensor_shapes(cfg)
     H, I, V = cfg.hidden, cfg.intermediate, cfg.vocab
     out: Dict[str, tuple] = {}
     for i in range(cfg.n_layers):
@@ -157,11 +161,38 @@ class RandomSource:
             if len(shape) == 1:
                 return 0.1 * t
             return t * (1.0 if name == "embed" else float(shape[1]) ** -0.5)
+        if self.cfg.family == "seledra":
+            return _seledra_init(name, shape, t)
         if is_norm_w:
             t = 1.0 + 0.05 * t
         else:
             t = 0.02 * t
         return t
+
+
+def _seledra_init(name: str, shape: tuple, t: torch.Tensor) -> torch.Tensor:
+    """Random Seledra tensors in ranges where every mechanism takes part: gains around one, visible biases, blending
+    weights away from 0 and 1, decays neither stuck at 1 nor at 0, fan-in scaling for the linear maps."""
+    leaf = name.split(".", 1)[1] if name.startswith("l") and "." in name else name
+    if leaf.endswith("norm") or leaf.endswith("norm1") or leaf.endswith("norm2"):
+        return 1.0 + 0.1 * t
+    if leaf == "mix.temp":
+        return 1.0 + 0.25 * t
+    if leaf == "mix.vmix":
+        return 0.35 + 0.1 * t
+    if leaf == "mix.A_log":
+        return -1.0 + 0.5 * t
+    if leaf in ("mix.dt_bias", "mlp.act"):
+        return 0.5 * t
+    if leaf.endswith(".conv"):
+        return t * 0.5
+    if leaf.endswith(".b") and len(shape) == 1:       # projection biases (the 2-D 'mix.b' is a linear map)
+        return 0.2 * t
+    if name == "embed":
+        return t
+    if name == "pos":
+        return 0.5 * t
+    return t * float(shape[-1]) ** -0.5
 
 
 class CheckpointSource:
@@ -222,12 +253,36 @@ def load_gigezen_layer(cfg, src, i: int, dtype: torch.dtype, device) -> Dict[str
     return out
 
 
-def _load_gigezen_span(cfg, src, start, end, need_embed, need_head, dtype, device) -> Dict[str, object]:
+def load_seledra_layer(cfg, src, i: int, dtype: torch.dtype, device) -> Dict[str, torch.Tensor]:
+    """Canonical tensors of one Seledra layer: linear maps ``[out, in]`` in ``dtype``; everything that enters a norm, a
+    gate of the recurrence or an activation's shape (gains, biases, temperatures, decay parameters, taps) in fp32."""
+    from ..models.seledra import SinkAttentionSpec
+
+    L, p = cfg.layers[i], f"l{i}."
+    mv = lambda n: src.get(p + n).to(device=device, dtype=dtype).contiguous()  # noqa: E731
+    f32 = lambda n: src.get(p + n).to(device=device, dtype=torch.float32).contiguous()  # noqa: E731
+    out = {"norm1_w": f32("norm1"), "q_w": mv("mix.q"), "k_w": mv("mix.k"), "v_w": mv("mix.v"), "g_w": mv("mix.g"),
+           "o_w": mv("mix.o")}
+    if isinstance(L.mixer, SinkAttentionSpec):
+        out.update(qkv_b=torch.cat([f32("mix.q.b"), f32("mix.k.b"), f32("mix.v.b")]), q_norm_w=f32("mix.q.norm"),
+                   k_norm_w=f32("mix.k.norm"), temp=f32("mix.temp"), vmix=f32("mix.vmix").reshape(1))
+    else:
+        out.update(conv_w=torch.cat([f32("mix.q.conv"), f32("mix.k.conv"), f32("mix.v.conv")], 0), b_w=mv("mix.b"),
+                   a_w=mv("mix.a"), A_log=f32("mix.A_log"), dt_bias=f32("mix.dt_bias"), o_norm_w=f32("mix.norm"))
+    if L.mlp is not None:
+        out.update(norm2_w=f32("norm2"), up_w=mv("mlp.up"), down_w=mv("mlp.down"), act=f32("mlp.act"))
+    return out
+
+
+def _load_layer_list_span(cfg, src, start, end, need_embed, need_head, dtype, device) -> Dict[str, object]:
     cfg.check_span(start, end)
-    out: Dict[str, object] = {"layers": [load_gigezen_layer(cfg, src, i, dtype, device) for i in range(start, end)],
+    per_layer = load_seledra_layer if cfg.family == "seledra" else load_gigezen_layer
+    out: Dict[str, object] = {"layers": [per_layer(cfg, src, i, dtype, device) for i in range(start, end)],
                               "start": start, "end": end, "has_embed": bool(need_embed), "has_head": bool(need_head)}
     if need_embed:
         out["embed"] = src.get("embed").to(device=device, dtype=dtype).contiguous()
+        if getattr(cfg, "learned_positions", False):
+            out["pos_embed"] = src.get("pos").to(device=device, dtype=dtype).contiguous()
     if need_head:
         out["final_norm_w"] = src.get("final.norm").to(device=device, dtype=torch.float32).contiguous()
         out["lm_head"] = src.get("head").to(device=device, dtype=dtype).contiguous()
@@ -240,8 +295,8 @@ def load_span(model: str, cfg: ModelConfig, start: int, end: int, *, need_embed:
     if not (0 <= start <= end <= cfg.n_layers):
         raise ValueError(f"bad span [{start}, {end}) for a {cfg.n_layers}-layer model")
     src = src or open_source(model, cfg, seed, device)
-    if cfg.family == "gigezen":
-        return _load_gigezen_span(cfg, src, start, end, need_embed, need_head, dtype, device)
+    if getattr(cfg, "layer_list", False):
+        return _load_layer_list_span(cfg, src, start, end, need_embed, need_head, dtype, device)
     out: Dict[str, object] = {"layers": [load_layer(cfg, src, i, dtype, device) for i in range(start, end)],
                               "start": start, "end": end, "has_embed": bool(need_embed),
                               "has_head": bool(need_head)}

@@ -375,6 +375,7 @@ typedef struct b200_add_norm_args {
     int32_t T, width, ldx, lda, ldb, ldp, top, ldo, out_dtype;
     float eps, gain_offset;
     int32_t pdl;
+    float add_scale;      /* x += add_scale * (add_a + add_b + pairs); a residual multiplier (1 = plain sum) */
 } b200_add_norm_args;
 int b200_add_rms_norm(const b200_add_norm_args* args, void* stream);
 
@@ -473,6 +474,103 @@ int b200_moe_scale(void* act, int32_t ld, int32_t dtype, const int32_t* ids, con
                    int32_t experts, int32_t ff, int32_t top, int32_t pdl, void* stream);
 int b200_moe_plan(const int32_t* ids, int32_t T, int32_t top, int32_t experts, int32_t* group_off, int32_t* row_pair,
                   int32_t* row_token, int32_t pdl, void* stream);
+
+/* Embedding gather to fp32 with a learned position vector added: out[t] = table[ids[t]] + pos_table[p_t],
+ * p_t = pos ? pos[t] : pos0 + t (clamped to the table). */
+int b200_embed_pos_f32(const void* ids, const void* table, const void* pos_table, int32_t table_dtype, const int32_t* pos,
+                       int32_t pos0, float* out, int32_t T, int32_t width, int32_t ldo, int32_t vocab, int32_t max_pos,
+                       int32_t pdl, void* stream);
+
+/* Piecewise activation of a feed-forward layer with two learned numbers (a_pos, a_neg: device floats at `params`):
+ *   z > 0:  softplus(a_pos) z^2 + lin z;     z <= 0:  (neg_base + softplus(a_neg)) (exp(z) - 1 - z) + lin z.
+ * z: fp32 [T, ff] (row stride ld); act: 16-bit or fp32 [T, ff] (row stride ldo). */
+int b200_xielu(const float* z, int32_t ld, const float* params, float lin, float neg_base, void* act, int32_t ldo,
+               int32_t out_dtype, int32_t T, int32_t ff, int32_t pdl, void* stream);
+
+/* Grouped-query softmax attention without rotation, with a sink in the denominator.
+ * proj[t] (fp32 row of the fused projection): q [heads x dim] at q_off, k [kv_heads x dim] at k_off, v [kv_heads x vdim] at
+ * v_off, one gate logit per head at g_off.
+ * Step 1, b200_sink_attn_append (one block per token): adds `bias` (q | k | v order, may be NULL); RMS-norms the WHOLE q
+ * row and the WHOLE k row (gains q_gain / k_gain, eps); folds scale * temp[h] into q (written back in place); divides every
+ * value head by its root mean square over vdim (eps, no gain); vmix_mode 1: leaves the values in v_first[t]; 2: v <- (1 - l)
+ * v + l v_first[t] with l = *vmix; then stores k and v as rows of the key / value planes at the token's position.
+ * Planes: one row [row_elems] per position, heads side by side; of token t: kv_ptrs ? kv_ptrs[t * kv_ptr_stride + {0, 1}]
+ * : k_cache / v_cache; position pos ? pos[t] : pos0 + t.
+ * Step 2, b200_sink_attn (one block per token, head and share): s_j = q . k_j for j <= position, weights
+ * exp(s_j) / (sink + sum_i exp(s_i)) (sink = 1: one more key of score 0 and no value; 0: plain softmax), fp32 throughout;
+ * out[t, h] = sigmoid(gate logit) * sum_j w_j v_j (16-bit or fp32, row stride ldo).  splits > 1 divides every token's
+ * keys over that many blocks which meet in `scratch` (b200_sink_attn_scratch_bytes) and are merged in index order. */
+typedef struct b200_sink_attn_args {
+    float* proj;
+    int32_t ldp, q_off, k_off, v_off, g_off;
+    const float* bias;
+    const float* q_gain;
+    const float* k_gain;
+    const float* temp;
+    const float* vmix;
+    float* v_first;
+    int32_t ldvf, vmix_mode;
+    void* k_cache;
+    void* v_cache;
+    const uint64_t* kv_ptrs;
+    const int32_t* pos;
+    int32_t kv_ptr_stride, pos0;
+    int32_t T, heads, kv_heads, dim, vdim, row_elems, cache_dtype;
+    float eps, scale, sink;
+    void* out;
+    int32_t ldo, out_dtype;
+    int32_t pdl, reserved;
+} b200_sink_attn_args;
+int b200_sink_attn_append(const b200_sink_attn_args* args, void* stream);
+int b200_sink_attn(const b200_sink_attn_args* args, int32_t splits, float* scratch, void* stream);
+int64_t b200_sink_attn_scratch_bytes(int32_t T, int32_t heads, int32_t vdim, int32_t splits);
+/* The same attention for a prompt-size chunk of ONE session on the tensor cores (16-bit caches, dim and vdim multiples
+ * of 16 up to 128): mma.sync m16n8k16 flash attention over the session's planes, scores and softmax fp32, the weights
+ * enter P.V as two 16-bit terms.  Queries as b200_sink_attn_append left them. */
+int b200_sink_attn_prefill(const b200_sink_attn_args* args, void* stream);
+
+/* Gated delta rule behind short causal convolutions.  Rows r = s * seq_len + i: token i of sequence s (a decode step has
+ * n_seq sequences of one token, a chunk of a prompt one sequence of seq_len tokens); position p = (pos ? pos[s] : pos0) + i.
+ * proj[r] (fp32 row of the fused projection): the convolutions' inputs [q | k | v] (kv_heads*dim, kv_heads*dim, heads*vdim
+ * channels) at c_off, one beta logit per head at b_off, one decay input per head at a_off.
+ * A sequence's state (fp32, at state_ptrs ? state_ptrs[s * state_ptr_stride] : state, plus state_off elements):
+ * [2][heads][dim][vdim] matrices - a launch whose first token is at p0 reads copy p0 & 1 (zeros when p0 = 0) and writes copy
+ * (p0 + seq_len) & 1 - followed by a ring [taps][channels] of convolution inputs, slot = position mod taps.
+ * Step 1, b200_delta_prep (one block per row): y_c = silu(sum_b w[c][taps-1-b] x_c(p - b)), inputs before the sequence's
+ * start are zero, inputs before the launch's first row come from the ring; q and k heads become unit vectors
+ * x / sqrt(sum x^2 + unit_eps), q also times dim^-1/2; beta = sigmoid(.), decay = exp(-exp(A_log) softplus(. + dt_bias)).
+ * work[r] = [q | k | v | beta | decay] (fp32, row stride ldw).
+ * Step 2, b200_delta_rule (sequential over a sequence's tokens, parallel over sequences, heads and columns):
+ *   S <- decay S;  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q      (head h uses q/k head h / (heads / kv_heads))
+ * o: fp32 [rows, heads * vdim] (row stride ldo).  Also stores the last rows' convolution inputs in the ring. */
+typedef struct b200_delta_args {
+    const float* proj;
+    int32_t ldp, c_off, b_off, a_off;
+    const float* conv_w;      /* fp32 [channels, taps] */
+    const float* A_log;
+    const float* dt_bias;
+    float* work;
+    int32_t ldw;
+    float* state;
+    const uint64_t* state_ptrs;
+    int32_t state_ptr_stride, reserved0;
+    int64_t state_off;
+    const int32_t* pos;
+    int32_t pos0;
+    int32_t n_seq, seq_len, heads, kv_heads, dim, vdim, taps;
+    float unit_eps;
+    float* o;
+    int32_t ldo, pdl;
+} b200_delta_args;
+int b200_delta_prep(const b200_delta_args* args, void* stream);
+int b200_delta_rule(const b200_delta_args* args, void* stream);
+
+/* Gated RMS norm per head: out[t, h, :] = o[t, h, :] / sqrt(mean(o^2) + eps) * gain[:] * silu(gate[t, h, :]).
+ * o: fp32 [T, heads * vdim] (ldo); gate: fp32 rows (ldg) holding heads * vdim logits; gain: fp32 [vdim] shared by the
+ * heads; out 16-bit or fp32 (ldout). */
+int b200_gated_head_norm(const float* o, int32_t ldo, const float* gate, int32_t ldg, const float* gain, void* out,
+                         int32_t ldout, int32_t out_dtype, int32_t T, int32_t heads, int32_t vdim, float eps, int32_t pdl,
+                         void* stream);
 
 #ifdef __cplusplus
 }

@@ -20,4 +20,4 @@ from petals_b200.runtime.stages import Stage0, StageLast, StageSegment, StageWei
 def load_stage_model(model_name: str, device, role: str, *, start: int = 0, end: Optional[int] = None,
                      dtype: torch.dtype = torch.float16, use_cpu_offload: bool = False, seed: int = 0) -> StageWeights:
     return load_stage_weights(model_name, device, role, start=start, end=end, dtype=dtype,
-                              use_cpu_offload=use_cpu_offload, seed=seed, families=("gpt2", "llama", "gigezen"))
+                              use_cpu_offload=use_cpu_offload, seed=seed, families=("gpt2", "llama", "gigezen", "seledra"))

@@ -33,7 +33,7 @@ def _ensure_library(cfg) -> None:
     sys.path.insert(0, os.path.join(root, "csrc"))
     import build as csrc_build
 
-    unit_set = "layered" if getattr(cfg, "family", "") == "gigezen" else None
+    unit_set = "layered" if getattr(cfg, "layer_list", False) else None
     native.LIB_PATH = csrc_build.build(unit_set=unit_set)
 
 
