@@ -7,6 +7,7 @@
 // One block = 64 consecutive queries of one head (4 warps x 16 rows), keys in tiles of 64; the next key / value tile is
 // fetched by cp.async into a second shared-memory buffer while the tensor cores work on the current one.
 #include "common.h"
+#include "mma.cuh"
 #include "ptx.cuh"
 
 namespace b200 {
@@ -23,34 +24,7 @@ struct LatentMmaParams {
     int vec;                  // sizes and addresses allow 16-byte tile loads
 };
 
-__device__ __forceinline__ void mma_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1, int is_bf16) {
-    if (is_bf16)
-        asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
-                     : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-                     : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-    else
-        asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
-                     : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-                     : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-}
-
-__device__ __forceinline__ uint32_t pack2(float lo, float hi, int is_bf16) {
-    return (uint32_t)float_to_h16(lo, is_bf16) | ((uint32_t)float_to_h16(hi, is_bf16) << 16);
-}
-
 constexpr int kQT = 64, kKT = 64;
-
-// 16-byte asynchronous copy global -> shared; bytes = 0 writes zeros (the source is not read)
-__device__ __forceinline__ void cp_async16(void* dst, const void* src, int bytes) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(smem_u32(dst)), "l"(src), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
-template <int N>
-__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory"); }
-// two 8x8 16-bit matrices, transposed on the way: lane l < 16 names row l % 8 of matrix l / 8
-__device__ __forceinline__ void ldmatrix_x2_trans(uint32_t& r0, uint32_t& r1, const void* row) {
-    asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];\n" : "=r"(r0), "=r"(r1) : "r"(smem_u32(row)));
-}
 
 // NV = value n-tiles of 8 columns (vdim <= 8 * NV)
 template <int NV>

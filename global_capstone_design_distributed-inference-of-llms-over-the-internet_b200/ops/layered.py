@@ -234,7 +234,7 @@ def sink_attn(a: SinkAttnArgs, splits: int = 1, scratch: Optional[torch.Tensor] 
 
 def sink_attn_prefill_fits(dim: int, vdim: int) -> bool:
     """Can the tensor-core kernel take heads of these sizes?"""
-    return hasattr(native.lib(), "b200_sink_attn_prefill") and dim % 16 == 0 and vdim % 16 == 0 and dim <= 128 and vdim <= 128
+    return dim <= 512 and vdim <= 256
 
 
 def sink_attn_prefill(a: SinkAttnArgs) -> None:

@@ -82,7 +82,7 @@ def save_file(tensors: Dict[str, torch.Tensor], path: str, metadata: Optional[Di
         f.write(hj)
         for k in order:
             t = tensors[k].detach().contiguous().cpu()
-            f.write(t.view(torch.uint8).numpy().tobytes() if t.numel() else b"")
+            f.write(t.reshape(-1).view(torch.uint8).numpy().tobytes() if t.numel() else b"")
 
 
 class CheckpointIndex:

@@ -524,8 +524,8 @@ typedef struct b200_sink_attn_args {
 int b200_sink_attn_append(const b200_sink_attn_args* args, void* stream);
 int b200_sink_attn(const b200_sink_attn_args* args, int32_t splits, float* scratch, void* stream);
 int64_t b200_sink_attn_scratch_bytes(int32_t T, int32_t heads, int32_t vdim, int32_t splits);
-/* The same attention for a prompt-size chunk of ONE session on the tensor cores (16-bit caches, dim and vdim multiples
- * of 16 up to 128): mma.sync m16n8k16 flash attention over the session's planes, scores and softmax fp32, the weights
+/* The same attention for a prompt-size chunk of ONE session on the tensor cores (16-bit caches and output, vdim <= 256;
+ * k_cache / v_cache and pos0, not the pointer table): mma.sync m16n8k16 flash attention over the session's planes, scores and softmax fp32, the weights
  * enter P.V as two 16-bit terms.  Queries as b200_sink_attn_append left them. */
 int b200_sink_attn_prefill(const b200_sink_attn_args* args, void* stream);
 
