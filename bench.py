@@ -57,7 +57,7 @@ def parse_args():
                     help="instead of the headline run: prefill / decode throughput of the layer-list design (Gigezen) beside "
                          "Llama at equal layer sizes (scripts/bench_designs.py), one JSON line per size and design")
     ap.add_argument("--design-sizes", default="small,7b")
-    ap.add_argument("--design-only", default="", help="comma list of designs to run (llama, gigezen)")
+    ap.add_argument("--design-only", default="", help="comma list of designs to run (llama, gigezen, seledra)")
     return ap.parse_args()
 
 

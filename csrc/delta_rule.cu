@@ -2,7 +2,7 @@
 // current value along the current key and is read with the query.  Everything here is fp32.
 //   prep  (one block per row):   convolutions + silu, unit-length q / k, beta and decay of every head
 //   rule  (sequential in time):  S <- decay S;  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q
-// A sequence's state lives with its cache: two copies of the heads' matrices (a launch whose first token is at position
+// A sequence's state lives with its cache: two copies of the heads' matrices, column-major (a launch whose first token is at position
 // p0 reads copy p0 & 1 and writes copy (p0 + n) & 1, so a step that is run twice leaves the same state) and a ring of
 // the convolutions' last inputs (slot = position mod taps).
 #include "common.h"
@@ -18,17 +18,23 @@ __device__ __forceinline__ float* delta_state(const b200_delta_args& a, int s) {
 __device__ __forceinline__ float softplus32(float x) { return fmaxf(x, 0.f) + log1pf(expf(-fabsf(x))); }
 
 // ------------------------------------------------------------------ prep
-__global__ void __launch_bounds__(256) delta_prep_kernel(b200_delta_args a) {
-    extern __shared__ float y[];                   // [channels] convolved + activated
+// One block per (row, unit); a unit is a query head with its key head (convolved, activated, made unit vectors, and
+// their dot product, which the read-out needs) or a value head (convolved and activated); the block of unit 0 also
+// evaluates beta and the decay of every head.
+__global__ void __launch_bounds__(128) delta_prep_kernel(b200_delta_args a) {
+    extern __shared__ float y[];                   // pair: q [dim] | k [dim]; value head: [vdim]
+    __shared__ float red[3][4];
     pdl_wait_prior_grid();
     pdl_launch_dependents();
-    const int r = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int r = blockIdx.x, unit = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int s = r / a.seq_len, i = r - s * a.seq_len;
     const int p = (a.pos ? a.pos[s] : a.pos0) + i;
-    const int qk = a.kv_heads * a.dim, C = 2 * qk + a.heads * a.vdim, taps = a.taps;
-    const float* ring = delta_state(a, s) + (size_t)2 * a.heads * a.dim * a.vdim;
+    const int D = a.dim, V = a.vdim, G = a.kv_heads, H = a.heads;
+    const int qk = G * D, C = 2 * qk + H * V, taps = a.taps;
+    const float* ring = delta_state(a, s) + (size_t)2 * H * D * V;
     const float* row = a.proj + (size_t)r * a.ldp + a.c_off;
-    for (int c = tid; c < C; c += 256) {
+    float* out = a.work + (size_t)r * a.ldw;
+    auto conv = [&](int c) {
         const float* w = a.conv_w + (size_t)c * taps;
         float acc = 0.f;
         for (int b = taps - 1; b >= 0; --b) {      // oldest input first
@@ -36,42 +42,77 @@ __global__ void __launch_bounds__(256) delta_prep_kernel(b200_delta_args a) {
             const float x = b <= i ? row[c - (ptrdiff_t)b * a.ldp] : ring[(size_t)((p - b) % taps) * C + c];
             acc = fmaf(w[taps - 1 - b], x, acc);
         }
-        y[c] = acc / (1.0f + expf(-acc));
-    }
-    __syncthreads();
-    float* out = a.work + (size_t)r * a.ldw;
-    const float qscale = rsqrtf((float)a.dim);
-    for (int hh = warp; hh < 2 * a.kv_heads; hh += 8) {      // q heads, then k heads
-        const float* src = y + hh * a.dim;
-        float ss = 0.f;
-        for (int d = lane; d < a.dim; d += 32) ss = fmaf(src[d], src[d], ss);
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-        const float f = (1.0f / sqrtf(ss + a.unit_eps)) * (hh < a.kv_heads ? qscale : 1.0f);
-        for (int d = lane; d < a.dim; d += 32) out[hh * a.dim + d] = src[d] * f;
-    }
-    for (int c = 2 * qk + tid; c < C; c += 256) out[c] = y[c];
-    for (int h = tid; h < a.heads; h += 256) {
+        return acc / (1.0f + expf(-acc));
+    };
+    if (unit == 0) {
         const float* rr = a.proj + (size_t)r * a.ldp;
-        out[C + h] = 1.0f / (1.0f + expf(-rr[a.b_off + h]));
-        out[C + a.heads + h] = expf(-expf(a.A_log[h]) * softplus32(rr[a.a_off + h] + a.dt_bias[h]));
+        for (int h = tid; h < H; h += 128) {
+            out[C + h] = 1.0f / (1.0f + expf(-rr[a.b_off + h]));
+            out[C + H + h] = expf(-expf(a.A_log[h]) * softplus32(rr[a.a_off + h] + a.dt_bias[h]));
+        }
     }
+    if (unit >= G) {                               // a value head
+        const int h = unit - G;
+        for (int d = tid; d < V; d += 128) out[2 * qk + h * V + d] = conv(2 * qk + h * V + d);
+        return;
+    }
+    const int g = unit;
+    float sq = 0.f, sk = 0.f;
+    for (int d = tid; d < D; d += 128) {
+        const float qv = conv(g * D + d), kv = conv(qk + g * D + d);
+        y[d] = qv;
+        y[D + d] = kv;
+        sq = fmaf(qv, qv, sq);
+        sk = fmaf(kv, kv, sk);
+    }
+    float dot = 0.f;
+    for (int d = tid; d < D; d += 128) dot = fmaf(y[d], y[D + d], dot);   // (each thread reads what it wrote)
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        sq += __shfl_xor_sync(0xffffffffu, sq, o);
+        sk += __shfl_xor_sync(0xffffffffu, sk, o);
+        dot += __shfl_xor_sync(0xffffffffu, dot, o);
+    }
+    if (lane == 0) red[0][warp] = sq, red[1][warp] = sk, red[2][warp] = dot;
+    __syncthreads();
+    sq = (red[0][0] + red[0][1]) + (red[0][2] + red[0][3]);
+    sk = (red[1][0] + red[1][1]) + (red[1][2] + red[1][3]);
+    dot = (red[2][0] + red[2][1]) + (red[2][2] + red[2][3]);
+    const float fq = (1.0f / sqrtf(sq + a.unit_eps)) * rsqrtf((float)D), fk = 1.0f / sqrtf(sk + a.unit_eps);
+    for (int d = tid; d < D; d += 128) {
+        out[g * D + d] = y[d] * fq;
+        out[qk + g * D + d] = y[D + d] * fk;
+    }
+    if (tid == 0) out[C + 2 * H + g] = dot * fq * fk;
 }
 
 // ------------------------------------------------------------------ rule
-constexpr int kDeltaCols = 64;       // columns of S per block (8 per warp)
-constexpr int kDeltaBatch = 16;      // tokens staged in shared memory at a time
+constexpr int kDeltaBatch = 16;      // tokens staged in shared memory at a time (two buffers)
 
-// Block = (sequence, head, 64 columns of S).  Lane = slice * 8 + column: column j's rows i = slice + 4 n are in the
-// registers of 4 lanes, dot products meet by two shuffles.
-template <int NR>
-__global__ void __launch_bounds__(256) delta_rule_kernel(b200_delta_args a) {
-    extern __shared__ float sm[];    // per staged token: k [dim] | q [dim] | v [64] | beta, decay
+__device__ __forceinline__ void cp_async4(void* dst, const void* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(smem_u32(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async16f(void* dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(smem_u32(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory"); }
+
+// Block = (sequence, head, 256 / SL columns of S).  Lane = column * SL + slice: column j's rows slice * NR .. + NR are in
+// the registers of one lane, the dot products over a column meet by log2(SL) shuffles.  The state is kept column-major
+// ([head][column][row]) so that a lane's rows are contiguous.  Tokens are staged 16 at a time by cp.async into one of
+// two buffers while the other one is being consumed.
+template <int NR, int SL>
+__global__ void __launch_bounds__(256) delta_rule_kernel(b200_delta_args a, int vec) {
+    extern __shared__ __align__(16) float sm[];
     pdl_wait_prior_grid();
     pdl_launch_dependents();
+    constexpr int Dp = NR * SL, COLS = 256 / SL, CPW = 32 / SL;
+    constexpr int STRIDE = 2 * Dp + COLS + 4;       // k | q | v columns | beta, decay, k.q, -
     const int s = blockIdx.x, h = blockIdx.y, tile = blockIdx.z;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int slice = lane >> 3, j = tile * kDeltaCols + warp * 8 + (lane & 7);
+    const int slice = lane % SL, cw = warp * CPW + lane / SL, j = tile * COLS + cw;
     const int D = a.dim, V = a.vdim, H = a.heads;
     const int g = h / (H / a.kv_heads);
     const int qk = a.kv_heads * D, C = 2 * qk + H * V;
@@ -80,68 +121,91 @@ __global__ void __launch_bounds__(256) delta_rule_kernel(b200_delta_args a) {
     float* st = delta_state(a, s);
     float S[NR];
     {
-        const float* src = st + ((size_t)(p0 & 1) * H + h) * D * V;
+        const float* src = st + (((size_t)(p0 & 1) * H + h) * V + j) * D;
 #pragma unroll
         for (int n = 0; n < NR; ++n) {
-            const int i = slice + 4 * n;
-            S[n] = (p0 > 0 && col && i < D) ? src[(size_t)i * V + j] : 0.f;
+            const int i = slice * NR + n;
+            S[n] = (p0 > 0 && col && i < D) ? src[i] : 0.f;
         }
     }
-    const int stride = 2 * D + kDeltaCols + 2;
-    for (int t0 = 0; t0 < a.seq_len; t0 += kDeltaBatch) {
+    for (int e = tid; e < 2 * kDeltaBatch * STRIDE; e += 256) sm[e] = 0.f;      // rows beyond dim stay zero
+    __syncthreads();
+    const int tok = tid >> 4, sub = tid & 15;        // 16 threads stage one token
+    auto stage = [&](int buf, int t0) {
         const int nb = a.seq_len - t0 < kDeltaBatch ? a.seq_len - t0 : kDeltaBatch;
-        __syncthreads();
-        for (int e = tid; e < nb * stride; e += 256) {
-            const int b = e / stride, c = e - b * stride;
-            const float* w = a.work + (size_t)(s * a.seq_len + t0 + b) * a.ldw;
-            float v;
-            if (c < D)
-                v = w[qk + g * D + c];                        // key
-            else if (c < 2 * D)
-                v = w[g * D + (c - D)];                       // query
-            else if (c < 2 * D + kDeltaCols) {
-                const int jj = tile * kDeltaCols + (c - 2 * D);
-                v = jj < V ? w[2 * qk + h * V + jj] : 0.f;    // value columns of this block
-            } else
-                v = w[C + (c - 2 * D - kDeltaCols) * H + h];  // beta, decay
-            sm[e] = v;
+        if (tok < nb) {
+            const float* w = a.work + (size_t)(s * a.seq_len + t0 + tok) * a.ldw;
+            float* dst = sm + (buf * kDeltaBatch + tok) * STRIDE;
+            if (vec) {
+                for (int c = sub * 4; c < D; c += 64) {
+                    cp_async16f(dst + c, w + qk + g * D + c);
+                    cp_async16f(dst + Dp + c, w + g * D + c);
+                }
+            } else {
+                for (int c = sub; c < D; c += 16) {
+                    cp_async4(dst + c, w + qk + g * D + c);
+                    cp_async4(dst + Dp + c, w + g * D + c);
+                }
+            }
+            for (int c = sub; c < COLS; c += 16)
+                if (tile * COLS + c < V) cp_async4(dst + 2 * Dp + c, w + 2 * qk + h * V + tile * COLS + c);
+            if (sub == 0) cp_async4(dst + 2 * Dp + COLS, w + C + h);
+            if (sub == 1) cp_async4(dst + 2 * Dp + COLS + 1, w + C + H + h);
+            if (sub == 2) cp_async4(dst + 2 * Dp + COLS + 2, w + C + 2 * H + g);
+        }
+        cp_commit();
+    };
+    stage(0, 0);
+    int buf = 0;
+    for (int t0 = 0; t0 < a.seq_len; t0 += kDeltaBatch, buf ^= 1) {
+        const int nb = a.seq_len - t0 < kDeltaBatch ? a.seq_len - t0 : kDeltaBatch;
+        if (t0 + kDeltaBatch < a.seq_len) {
+            stage(buf ^ 1, t0 + kDeltaBatch);
+            cp_wait<1>();
+        } else {
+            cp_wait<0>();
         }
         __syncthreads();
         for (int b = 0; b < nb; ++b) {
-            const float* kk = sm + b * stride;
-            const float* qq = kk + D;
-            const float vj = kk[2 * D + warp * 8 + (lane & 7)];
-            const float beta = kk[2 * D + kDeltaCols], dec = kk[2 * D + kDeltaCols + 1];
-            float dk = 0.f, dq = 0.f, kq = 0.f;
+            const float* kk = sm + (buf * kDeltaBatch + b) * STRIDE + slice * NR;
+            const float* qq = kk + Dp;
+            const float* sc = sm + (buf * kDeltaBatch + b) * STRIDE + 2 * Dp;
+            float kr[NR];
+            float dk0 = 0.f, dk1 = 0.f, dq0 = 0.f, dq1 = 0.f;
 #pragma unroll
-            for (int n = 0; n < NR; ++n) {
-                const int i = slice + 4 * n;
-                const float ki = i < D ? kk[i] : 0.f, qi = i < D ? qq[i] : 0.f;
-                dk = fmaf(S[n], ki, dk);
-                dq = fmaf(S[n], qi, dq);
-                kq = fmaf(ki, qi, kq);
+            for (int n = 0; n < NR; n += 4) {
+                const float4 k4 = *reinterpret_cast<const float4*>(kk + n);
+                const float4 q4 = *reinterpret_cast<const float4*>(qq + n);
+                kr[n] = k4.x, kr[n + 1] = k4.y, kr[n + 2] = k4.z, kr[n + 3] = k4.w;
+                dk0 = fmaf(S[n], k4.x, dk0);
+                dk1 = fmaf(S[n + 1], k4.y, dk1);
+                dk0 = fmaf(S[n + 2], k4.z, dk0);
+                dk1 = fmaf(S[n + 3], k4.w, dk1);
+                dq0 = fmaf(S[n], q4.x, dq0);
+                dq1 = fmaf(S[n + 1], q4.y, dq1);
+                dq0 = fmaf(S[n + 2], q4.z, dq0);
+                dq1 = fmaf(S[n + 3], q4.w, dq1);
             }
-            dk += __shfl_xor_sync(0xffffffffu, dk, 8);
-            dq += __shfl_xor_sync(0xffffffffu, dq, 8);
-            kq += __shfl_xor_sync(0xffffffffu, kq, 8);
-            dk += __shfl_xor_sync(0xffffffffu, dk, 16);
-            dq += __shfl_xor_sync(0xffffffffu, dq, 16);
-            kq += __shfl_xor_sync(0xffffffffu, kq, 16);
+            float dk = dk0 + dk1, dq = dq0 + dq1;
+#pragma unroll
+            for (int o = 1; o < SL; o <<= 1) {
+                dk += __shfl_xor_sync(0xffffffffu, dk, o);
+                dq += __shfl_xor_sync(0xffffffffu, dq, o);
+            }
+            const float vj = sc[cw], beta = sc[COLS], dec = sc[COLS + 1], kq = sc[COLS + 2];
             const float u = beta * (vj - dec * dk);
 #pragma unroll
-            for (int n = 0; n < NR; ++n) {
-                const int i = slice + 4 * n;
-                S[n] = fmaf(i < D ? kk[i] : 0.f, u, dec * S[n]);
-            }
+            for (int n = 0; n < NR; ++n) S[n] = fmaf(kr[n], u, dec * S[n]);
             if (slice == 0 && col) a.o[(size_t)(s * a.seq_len + t0 + b) * a.ldo + (size_t)h * V + j] = fmaf(u, kq, dec * dq);
         }
+        __syncthreads();                           // the buffer is free for the copies after the next ones
     }
-    {
-        float* dst = st + ((size_t)((p0 + a.seq_len) & 1) * H + h) * D * V;
+    if (col) {
+        float* dst = st + (((size_t)((p0 + a.seq_len) & 1) * H + h) * V + j) * D;
 #pragma unroll
         for (int n = 0; n < NR; ++n) {
-            const int i = slice + 4 * n;
-            if (col && i < D) dst[(size_t)i * V + j] = S[n];
+            const int i = slice * NR + n;
+            if (i < D) dst[i] = S[n];
         }
     }
     if (h == 0 && tile == 0) {       // the convolutions' inputs of the last rows go to the ring
@@ -155,11 +219,16 @@ __global__ void __launch_bounds__(256) delta_rule_kernel(b200_delta_args a) {
     }
 }
 
-template <int NR>
+template <int NR, int SL>
 static int launch_delta_rule(const b200_delta_args* a, cudaStream_t s) {
-    const size_t smem = (size_t)kDeltaBatch * (2 * a->dim + kDeltaCols + 2) * sizeof(float);
-    dim3 grid(a->n_seq, a->heads, (a->vdim + kDeltaCols - 1) / kDeltaCols);
-    B200_CUDA_CHECK(launch(delta_rule_kernel<NR>, grid, dim3(256), smem, s, a->pdl != 0, *a));
+    constexpr int COLS = 256 / SL;
+    const size_t smem = (size_t)2 * kDeltaBatch * (2 * NR * SL + COLS + 4) * sizeof(float);
+    if (smem > 48 * 1024)
+        B200_CUDA_CHECK(cudaFuncSetAttribute(delta_rule_kernel<NR, SL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    const int qk = a->kv_heads * a->dim;
+    const int vec = (a->dim % 4 == 0 && a->ldw % 4 == 0 && qk % 4 == 0 && (reinterpret_cast<uintptr_t>(a->work) & 15) == 0) ? 1 : 0;
+    dim3 grid(a->n_seq, a->heads, (a->vdim + COLS - 1) / COLS);
+    B200_CUDA_CHECK(launch(delta_rule_kernel<NR, SL>, grid, dim3(256), smem, s, a->pdl != 0, *a, vec));
     return B200_OK;
 }
 
@@ -180,12 +249,10 @@ static int check_delta(const b200_delta_args* a, const char* who) {
 extern "C" int b200_delta_prep(const b200_delta_args* a, void* stream) {
     if (int rc = check_delta(a, "b200_delta_prep")) return rc;
     if (!a->conv_w || !a->A_log || !a->dt_bias) return fail(B200_EINVAL, "b200_delta_prep: parameters missing");
-    const size_t smem = (size_t)(2 * a->kv_heads * a->dim + a->heads * a->vdim) * sizeof(float);
-    if (smem > 200 * 1024) return fail(B200_ELIMIT, "b200_delta_prep: %zu B of channels exceed shared memory", smem);
-    if (smem > 48 * 1024)
-        B200_CUDA_CHECK(cudaFuncSetAttribute(delta_prep_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    B200_CUDA_CHECK(launch(delta_prep_kernel, dim3(a->n_seq * a->seq_len), dim3(256), smem, static_cast<cudaStream_t>(stream),
-                           a->pdl != 0, *a));
+    const size_t smem = (size_t)(2 * a->dim > a->vdim ? 2 * a->dim : a->vdim) * sizeof(float);
+    if (smem > 48 * 1024) return fail(B200_ELIMIT, "b200_delta_prep: dim %d exceeds shared memory", a->dim);
+    B200_CUDA_CHECK(launch(delta_prep_kernel, dim3(a->n_seq * a->seq_len, a->kv_heads + a->heads), dim3(128), smem,
+                           static_cast<cudaStream_t>(stream), a->pdl != 0, *a));
     return B200_OK;
 }
 
@@ -193,10 +260,9 @@ extern "C" int b200_delta_rule(const b200_delta_args* a, void* stream) {
     if (int rc = check_delta(a, "b200_delta_rule")) return rc;
     if (!a->o) return fail(B200_EINVAL, "b200_delta_rule: o missing");
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    const int nr = (a->dim + 3) / 4;
-    if (nr <= 8) return launch_delta_rule<8>(a, s);
-    if (nr <= 16) return launch_delta_rule<16>(a, s);
-    if (nr <= 32) return launch_delta_rule<32>(a, s);
-    if (nr <= 64) return launch_delta_rule<64>(a, s);
-    return fail(B200_ELIMIT, "b200_delta_rule: dim %d > 256", a->dim);
+    if (a->dim <= 64) return launch_delta_rule<8, 8>(a, s);
+    if (a->dim <= 128) return launch_delta_rule<8, 16>(a, s);
+    if (a->dim <= 256) return launch_delta_rule<16, 16>(a, s);
+    if (a->dim <= 512) return launch_delta_rule<32, 16>(a, s);
+    return fail(B200_ELIMIT, "b200_delta_rule: dim %d > 512", a->dim);
 }

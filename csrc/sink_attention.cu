@@ -24,7 +24,8 @@ __device__ __forceinline__ float block_sum_256(float v, float* red) {
     return tot;
 }
 
-// ------------------------------------------------------------------ norms + cache append (one block per token)
+// ------------------------------------------------------------------ norms + cache append
+// Three blocks per token: queries, keys, values (each is a chain of dependent passes over its part of the row).
 __global__ void __launch_bounds__(256) sink_attn_append_kernel(b200_sink_attn_args a) {
     __shared__ float red[8];
     pdl_wait_prior_grid();
@@ -35,36 +36,40 @@ __global__ void __launch_bounds__(256) sink_attn_append_kernel(b200_sink_attn_ar
     const int qn = a.heads * a.dim, kn = a.kv_heads * a.dim, vn = a.kv_heads * a.vdim;
     const bool f32 = a.cache_dtype == B200_F32;
     const int bf = a.cache_dtype == B200_BF16;
-    // queries: bias, one norm over the whole row, score scale and the head's temperature folded in
-    float* q = row + a.q_off;
-    float ss = 0.f;
-    for (int c = tid; c < qn; c += 256) {
-        const float v = q[c] + (a.bias ? a.bias[c] : 0.f);
-        q[c] = v;
-        ss = fmaf(v, v, ss);
-    }
-    float rstd = 1.0f / sqrtf(block_sum_256(ss, red) / (float)qn + a.eps);
-    for (int c = tid; c < qn; c += 256) {
-        const int h = c / a.dim;
-        q[c] = q[c] * rstd * a.q_gain[c] * (a.scale * (a.temp ? a.temp[h] : 1.0f));
-    }
-    // keys
-    float* k = row + a.k_off;
-    ss = 0.f;
-    for (int c = tid; c < kn; c += 256) {
-        const float v = k[c] + (a.bias ? a.bias[qn + c] : 0.f);
-        k[c] = v;
-        ss = fmaf(v, v, ss);
-    }
-    rstd = 1.0f / sqrtf(block_sum_256(ss, red) / (float)kn + a.eps);
     const size_t row_bytes = (size_t)a.row_elems * (f32 ? 4 : 2);
-    char* kd = sink_plane(a, t, 0) + (size_t)p * row_bytes;
-    for (int c = tid; c < kn; c += 256) {
-        const float v = k[c] * rstd * a.k_gain[c];
-        if (f32)
-            reinterpret_cast<float*>(kd)[c] = v;
-        else
-            reinterpret_cast<uint16_t*>(kd)[c] = float_to_h16(v, bf);
+    if (blockIdx.y == 0) {     // queries: bias, one norm over the whole row, score scale and the head's temperature folded in
+        float* q = row + a.q_off;
+        float ss = 0.f;
+        for (int c = tid; c < qn; c += 256) {
+            const float v = q[c] + (a.bias ? a.bias[c] : 0.f);
+            q[c] = v;
+            ss = fmaf(v, v, ss);
+        }
+        const float rstd = 1.0f / sqrtf(block_sum_256(ss, red) / (float)qn + a.eps);
+        for (int c = tid; c < qn; c += 256) {
+            const int h = c / a.dim;
+            q[c] = q[c] * rstd * a.q_gain[c] * (a.scale * (a.temp ? a.temp[h] : 1.0f));
+        }
+        return;
+    }
+    if (blockIdx.y == 1) {     // keys
+        float* k = row + a.k_off;
+        float ss = 0.f;
+        for (int c = tid; c < kn; c += 256) {
+            const float v = k[c] + (a.bias ? a.bias[qn + c] : 0.f);
+            k[c] = v;
+            ss = fmaf(v, v, ss);
+        }
+        const float rstd = 1.0f / sqrtf(block_sum_256(ss, red) / (float)kn + a.eps);
+        char* kd = sink_plane(a, t, 0) + (size_t)p * row_bytes;
+        for (int c = tid; c < kn; c += 256) {
+            const float v = k[c] * rstd * a.k_gain[c];
+            if (f32)
+                reinterpret_cast<float*>(kd)[c] = v;
+            else
+                reinterpret_cast<uint16_t*>(kd)[c] = float_to_h16(v, bf);
+        }
+        return;
     }
     // values: one warp per head at a time
     char* vd = sink_plane(a, t, 1) + (size_t)p * row_bytes;
@@ -134,23 +139,41 @@ __global__ void __launch_bounds__(kSinkWarps * 32) sink_attn_kernel(b200_sink_at
     for (int j0 = lo + warp * 32; j0 <= hi; j0 += kSinkWarps * 32) {
         const int n = hi - j0 + 1 < 32 ? hi - j0 + 1 : 32;
         float s = -INFINITY;
-        if (lane < n) {
-            float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;
-            if (vec16) {
-                const uint4* kr = reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(kb) + (size_t)(j0 + lane) * re + (size_t)g * D);
-                for (int c = 0; c < D / 8; ++c) {
-                    const uint4 v = kr[c];
-                    const float* qq = qs + c * 8;
-                    d0 = fmaf(qq[0], h16_to_float((uint16_t)(v.x & 0xffff), bf), d0);
-                    d1 = fmaf(qq[1], h16_to_float((uint16_t)(v.x >> 16), bf), d1);
-                    d2 = fmaf(qq[2], h16_to_float((uint16_t)(v.y & 0xffff), bf), d2);
-                    d3 = fmaf(qq[3], h16_to_float((uint16_t)(v.y >> 16), bf), d3);
-                    d0 = fmaf(qq[4], h16_to_float((uint16_t)(v.z & 0xffff), bf), d0);
-                    d1 = fmaf(qq[5], h16_to_float((uint16_t)(v.z >> 16), bf), d1);
-                    d2 = fmaf(qq[6], h16_to_float((uint16_t)(v.w & 0xffff), bf), d2);
-                    d3 = fmaf(qq[7], h16_to_float((uint16_t)(v.w >> 16), bf), d3);
+        if (vec16) {
+            // 8 lanes share a key (128 contiguous bytes per pass), 4 keys per instruction; lane L ends up with the score
+            // of key L, which pass L / 4 computed in subgroup L % 4
+            const int part = lane & 7, sg = lane >> 3;
+            const uint16_t* kbase = reinterpret_cast<const uint16_t*>(kb) + (size_t)g * D;
+#pragma unroll 2
+            for (int it = 0; it < 8; ++it) {
+                const int jj = it * 4 + sg;
+                float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;
+                if (jj < n) {
+                    const uint16_t* kr = kbase + (size_t)(j0 + jj) * re;
+                    for (int c = part * 8; c < D; c += 64) {
+                        const uint4 v = *reinterpret_cast<const uint4*>(kr + c);
+                        const float4 qa = *reinterpret_cast<const float4*>(qs + c), qb = *reinterpret_cast<const float4*>(qs + c + 4);
+                        d0 = fmaf(qa.x, h16_to_float((uint16_t)(v.x & 0xffff), bf), d0);
+                        d1 = fmaf(qa.y, h16_to_float((uint16_t)(v.x >> 16), bf), d1);
+                        d2 = fmaf(qa.z, h16_to_float((uint16_t)(v.y & 0xffff), bf), d2);
+                        d3 = fmaf(qa.w, h16_to_float((uint16_t)(v.y >> 16), bf), d3);
+                        d0 = fmaf(qb.x, h16_to_float((uint16_t)(v.z & 0xffff), bf), d0);
+                        d1 = fmaf(qb.y, h16_to_float((uint16_t)(v.z >> 16), bf), d1);
+                        d2 = fmaf(qb.z, h16_to_float((uint16_t)(v.w & 0xffff), bf), d2);
+                        d3 = fmaf(qb.w, h16_to_float((uint16_t)(v.w >> 16), bf), d3);
+                    }
                 }
-            } else {
+                float d = (d0 + d1) + (d2 + d3);
+                d += __shfl_xor_sync(0xffffffffu, d, 1);
+                d += __shfl_xor_sync(0xffffffffu, d, 2);
+                d += __shfl_xor_sync(0xffffffffu, d, 4);
+                const float got = __shfl_sync(0xffffffffu, d, (lane & 3) * 8);
+                if ((lane >> 2) == it) s = got;
+            }
+            if (lane >= n) s = -INFINITY;
+        } else if (lane < n) {
+            float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;
+            {
                 const size_t base = (size_t)(j0 + lane) * re + (size_t)g * D;
                 int d = 0;
                 for (; d + 4 <= D; d += 4) {
@@ -312,7 +335,7 @@ extern "C" int b200_sink_attn_append(const b200_sink_attn_args* a, void* stream)
     if (!a->q_gain || !a->k_gain) return fail(B200_EINVAL, "b200_sink_attn_append: norm gains missing");
     if (a->vmix_mode < 0 || a->vmix_mode > 2 || (a->vmix_mode && !a->v_first) || (a->vmix_mode == 2 && !a->vmix))
         return fail(B200_EINVAL, "b200_sink_attn_append: value blending without its operands");
-    B200_CUDA_CHECK(launch(sink_attn_append_kernel, dim3(a->T), dim3(256), 0, static_cast<cudaStream_t>(stream), a->pdl != 0, *a));
+    B200_CUDA_CHECK(launch(sink_attn_append_kernel, dim3(a->T, 3), dim3(256), 0, static_cast<cudaStream_t>(stream), a->pdl != 0, *a));
     return B200_OK;
 }
 

@@ -115,11 +115,31 @@ __device__ __forceinline__ float softplus_f(float x) { return fmaxf(x, 0.f) + lo
 
 __global__ void __launch_bounds__(256) xielu_kernel(const float* __restrict__ z, int ld, const float* __restrict__ params,
                                                    float lin, float neg_base, void* __restrict__ act, int ldo, int out_dtype,
-                                                   int T, int ff) {
+                                                   int T, int ff, int vec) {
     pdl_wait_prior_grid();
     pdl_launch_dependents();
     const float ap = softplus_f(params[0]), an = neg_base + softplus_f(params[1]);
     const size_t n = (size_t)T * ff;
+    if (vec) {      // four values per thread: 16-byte loads, 8-byte (16-bit output) or 16-byte stores
+        const int q = ff / 4;
+        for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < (size_t)T * q; i += (size_t)gridDim.x * blockDim.x) {
+            const int t = (int)(i / q), c = (int)(i - (size_t)t * q) * 4;
+            const float4 v = *reinterpret_cast<const float4*>(z + (size_t)t * ld + c);
+            float y[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int k = 0; k < 4; ++k) y[k] = y[k] > 0.f ? fmaf(ap * y[k], y[k], lin * y[k]) : fmaf(an, expm1f(y[k]) - y[k], lin * y[k]);
+            if (out_dtype == B200_F32) {
+                *reinterpret_cast<float4*>(static_cast<float*>(act) + (size_t)t * ldo + c) = make_float4(y[0], y[1], y[2], y[3]);
+            } else {
+                const int bf = out_dtype == B200_BF16;
+                uint2 o;
+                o.x = (uint32_t)float_to_h16(y[0], bf) | ((uint32_t)float_to_h16(y[1], bf) << 16);
+                o.y = (uint32_t)float_to_h16(y[2], bf) | ((uint32_t)float_to_h16(y[3], bf) << 16);
+                *reinterpret_cast<uint2*>(static_cast<uint16_t*>(act) + (size_t)t * ldo + c) = o;
+            }
+        }
+        return;
+    }
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
         const int t = (int)(i / ff), c = (int)(i - (size_t)t * ff);
         const float v = z[(size_t)t * ld + c];
@@ -168,10 +188,12 @@ extern "C" int b200_embed_pos_f32(const void* ids, const void* table, const void
 extern "C" int b200_xielu(const float* z, int32_t ld, const float* params, float lin, float neg_base, void* act, int32_t ldo,
                           int32_t out_dtype, int32_t T, int32_t ff, int32_t pdl, void* stream) {
     if (!z || !params || !act || T <= 0 || ff <= 0) return fail(B200_EINVAL, "b200_xielu: bad argument");
-    const size_t n = (size_t)T * ff;
+    const int vec = (ff % 4 == 0 && ld % 4 == 0 && ldo % 4 == 0 && (reinterpret_cast<uintptr_t>(z) & 15) == 0 &&
+                     (reinterpret_cast<uintptr_t>(act) & 15) == 0) ? 1 : 0;
+    const size_t n = (size_t)T * ff / (vec ? 4 : 1);
     const int blocks = (int)((n + 255) / 256 < 4096 ? (n + 255) / 256 : 4096);
     B200_CUDA_CHECK(launch(xielu_kernel, dim3(blocks), dim3(256), 0, static_cast<cudaStream_t>(stream), pdl != 0, z, ld, params,
-                           lin, neg_base, act, ldo, out_dtype, T, ff));
+                           lin, neg_base, act, ldo, out_dtype, T, ff, vec));
     return B200_OK;
 }
 

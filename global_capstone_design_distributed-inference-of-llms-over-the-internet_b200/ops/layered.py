@@ -249,7 +249,7 @@ def delta_args(proj: torch.Tensor, *, c_off: int, b_off: int, a_off: int, conv_w
                pos: Optional[torch.Tensor] = None, pos0: int = 0, pdl: bool = False) -> DeltaArgs:
     for t in (proj, conv_w, A_log, dt_bias, work, o, state):
         assert t is None or t.dtype == torch.float32
-    assert work.shape[1] >= 2 * kv_heads * dim + heads * vdim + 2 * heads
+    assert work.shape[1] >= 2 * kv_heads * dim + heads * vdim + 2 * heads + kv_heads
     a = DeltaArgs()
     a.proj, a.ldp, a.c_off, a.b_off, a.a_off = proj.data_ptr(), proj.stride(0), c_off, b_off, a_off
     a.conv_w, a.A_log, a.dt_bias = conv_w.data_ptr(), A_log.data_ptr(), dt_bias.data_ptr()

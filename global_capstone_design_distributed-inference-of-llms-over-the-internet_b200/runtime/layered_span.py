@@ -186,8 +186,8 @@ class LayeredSpan(NativeSpan):
                                  mx(lambda P: P["spec"].mixer.heads * ((P["spec"].mixer.kv_rank if latent(P) else
                                                                         getattr(P["spec"].mixer, "vdim", 0)) + 2)))
             deltas = [P["spec"].mixer for P in self.layers if isinstance(P["spec"].mixer, SD.DeltaRuleSpec)]
-            if deltas:     # what the recurrence reads (q | k | v | beta | decay) and its raw read-out, fp32
-                self.delta_work = f32(Tm, max(d.conv_channels + 2 * d.heads for d in deltas))
+            if deltas:     # what the recurrence reads (q | k | v | beta | decay | k.q) and its raw read-out, fp32
+                self.delta_work = f32(Tm, max((d.conv_channels + 2 * d.heads + d.kv_heads + 3) // 4 * 4 for d in deltas))
                 self.delta_o = f32(Tm, max(d.v_size for d in deltas))
             vm = [P["spec"].mixer for P in self.layers if getattr(P["spec"].mixer, "v_mix", False)]
             self.v_first = f32(Tm, max(v.v_size for v in vm)) if vm else None

@@ -1,8 +1,9 @@
-"""Prefill and decode throughput of the layer-list design (Gigezen) beside the closest uniform family (Llama) at equal
-layer sizes, random weights, one GPU.  Run as ``python bench.py --designs [--design-sizes small,7b] [--design-only X]``.
+"""Prefill and decode throughput of the layer-list designs (Gigezen, Seledra) beside the closest uniform family (Llama) at
+equal layer sizes, random weights, one GPU.  Run as ``python bench.py --designs [--design-sizes small,7b] [--design-only X]``.
 
-Per size: both models get the same width, head count, query/key width per head (Gigezen: unrotated + rotated), dense
-feed-forward width, layer count and vocabulary.  Timed with CUDA events on the launching stream after warm-up; a prefill
+Per size: the models get the same width, head count, query/key width per head (Gigezen: unrotated + rotated), dense
+feed-forward width, layer count and vocabulary.  Seledra: attention and delta-rule layers alternate (attention, delta,
+delta, attention), every layer with a feed-forward, as many key/value heads as query heads like the Llama beside it.  Timed with CUDA events on the launching stream after warm-up; a prefill
 pass streams every weight of the span and more activations than the L2 holds at 2048 tokens; decode steps are graph
 replays whose weights alone exceed the L2 from the "7b" size on (the "small" size is L2-resident and says so).
 One JSON line per (size, design).
@@ -23,12 +24,17 @@ VOCAB = 32000
 def _configs(s):
     from petals_b200.models.config import ModelConfig
     from petals_b200.models.gigezen import make_config
+    from petals_b200.models.seledra import make_config as make_seledra
 
     llama = ModelConfig("llama", s["layers"], s["hidden"], s["heads"], s["heads"], 128, s["ff"], VOCAB, name="llama-like")
     gz = make_config(n_layers=s["layers"], hidden=s["hidden"], vocab=VOCAB, heads=s["heads"], dim=64, rot_dim=64, vdim=128,
                      kv_rank=512, window=s["window"], ff=s["ff"], experts=8, top=2, groups=4, keep=2,
                      expert_ff=s["ff"] // 4 // 64 * 64, share_every=2, moe_every=2, limit=7.0, name="gigezen-like")
-    return {"llama": llama, "gigezen": gz}
+    sd = make_seledra("ADDA"[:s["layers"]] if s["layers"] <= 4 else "ADDA" * (s["layers"] // 4), hidden=s["hidden"], vocab=VOCAB,
+                      heads=s["heads"], kv_heads=s["heads"], dim=128, vdim=128, delta_heads=s["heads"], delta_kv_heads=s["heads"],
+                      delta_dim=128, delta_vdim=128, conv=4, ff=s["ff"], v_mix=True, residual_mult=0.5, max_positions=8192,
+                      name="seledra-like")
+    return {"llama": llama, "gigezen": gz, "seledra": sd}
 
 
 def _time(fn, reps, warm=3):

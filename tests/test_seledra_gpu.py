@@ -332,7 +332,7 @@ def _delta_reference(x, conv_w, blog, alog, A_log, dt_bias, H, G, dk, dv, unit_e
     return work, read
 
 
-@pytest.mark.parametrize("H,G,dk,dv,taps", [(4, 2, 24, 40, 3), (3, 3, 20, 12, 1), (2, 1, 72, 136, 5), (2, 2, 130, 8, 2)])
+@pytest.mark.parametrize("H,G,dk,dv,taps", [(4, 2, 24, 40, 3), (3, 3, 20, 12, 1), (2, 1, 72, 136, 5), (2, 2, 130, 8, 2), (2, 1, 260, 20, 4)])
 @pytest.mark.parametrize("cuts", [(57,), (1, 1, 1, 2, 17, 16, 15, 4), (33, 24)], ids=["whole", "pieces", "two"])
 def test_delta_rule_in_pieces_carries_state_and_convolution_inputs(H, G, dk, dv, taps, cuts):
     """The recurrence over one sequence cut into launches of many sizes (one token, two, the kernel's 16-token batches
@@ -349,7 +349,7 @@ def test_delta_rule_in_pieces_carries_state_and_convolution_inputs(H, G, dk, dv,
     proj = torch.cat([torch.zeros(T, 2), x, blog, alog], 1).to(DEV).contiguous()
     pad = 5
     state = torch.full((pad + 2 * H * dk * dv + taps * C,), 7.0, device=DEV)     # stale numbers: position 0 must not read them
-    work, o = torch.zeros(T, C + 2 * H, device=DEV), torch.zeros(T, H * dv, device=DEV)
+    work, o = torch.zeros(T, C + 2 * H + G, device=DEV), torch.zeros(T, H * dv, device=DEV)
     at = 0
     for n in cuts:
         a = L.delta_args(proj[at:at + n], c_off=2, b_off=2 + C, a_off=2 + C + H, conv_w=conv_w.to(DEV), A_log=A_log.to(DEV),
@@ -358,7 +358,9 @@ def test_delta_rule_in_pieces_carries_state_and_convolution_inputs(H, G, dk, dv,
         L.delta_prep(a)
         L.delta_rule(a)
         at += n
-    assert torch.allclose(work.cpu().double(), want_work, atol=2e-5, rtol=1e-5)
+    assert torch.allclose(work[:, :C + 2 * H].cpu().double(), want_work, atol=2e-5, rtol=1e-5)
+    kq = (want_work[:, :G * dk].view(T, G, dk) * want_work[:, G * dk:2 * G * dk].view(T, G, dk)).sum(-1)
+    assert torch.allclose(work[:, C + 2 * H:].cpu().double(), kq, atol=2e-6)
     assert torch.allclose(o.cpu().double().view(T, H, dv), want_read, atol=2e-5, rtol=1e-4)
     assert float((state[:pad] - 7.0).abs().max()) == 0
 
@@ -384,14 +386,14 @@ def test_delta_rule_step_for_a_batch_of_sequences_is_repeatable():
     for s, n, st in zip(seqs, lens, states):                                      # everything but the last token
         if n > 1:
             p = s[:n - 1].to(DEV).contiguous()
-            a = L.delta_args(p, work=torch.zeros(n - 1, C + 2 * H, device=DEV), o=torch.zeros(n - 1, H * dv, device=DEV), n_seq=1,
+            a = L.delta_args(p, work=torch.zeros(n - 1, C + 2 * H + G, device=DEV), o=torch.zeros(n - 1, H * dv, device=DEV), n_seq=1,
                              seq_len=n - 1, state=st, pos0=0, **par)
             L.delta_prep(a)
             L.delta_rule(a)
     last = torch.stack([s[-1] for s in seqs]).to(DEV).contiguous()
     ptrs = torch.tensor([[st.data_ptr(), 0] for st in states], dtype=torch.int64, device=DEV)
     pos = torch.tensor([n - 1 for n in lens], dtype=torch.int32, device=DEV)
-    work, o = torch.zeros(3, C + 2 * H, device=DEV), torch.zeros(3, H * dv, device=DEV)
+    work, o = torch.zeros(3, C + 2 * H + G, device=DEV), torch.zeros(3, H * dv, device=DEV)
     a = L.delta_args(last, work=work, o=o, n_seq=3, seq_len=1, state_ptrs=ptrs, state_ptr_stride=2, pos=pos, **par)
     L.delta_prep(a)
     L.delta_rule(a)
