@@ -18,16 +18,21 @@ __device__ __forceinline__ float* delta_state(const b200_delta_args& a, int s) {
 __device__ __forceinline__ float softplus32(float x) { return fmaxf(x, 0.f) + log1pf(expf(-fabsf(x))); }
 
 // ------------------------------------------------------------------ prep
-// One block per (row, unit); a unit is a query head with its key head (convolved, activated, made unit vectors, and
-// their dot product, which the read-out needs) or a value head (convolved and activated); the block of unit 0 also
-// evaluates beta and the decay of every head.
-__global__ void __launch_bounds__(128) delta_prep_kernel(b200_delta_args a) {
+// One block per (group of consecutive rows of a sequence, unit); a unit is a query head with its key head (convolved,
+// activated, made unit vectors, and their dot product, which the read-out needs) or a value head (convolved and
+// activated); the block of unit 0 also evaluates beta and the decay of every head.
+__global__ void __launch_bounds__(128) delta_prep_kernel(b200_delta_args a, int rows_per_block) {
     extern __shared__ float y[];                   // pair: q [dim] | k [dim]; value head: [vdim]
     __shared__ float red[3][4];
     pdl_wait_prior_grid();
     pdl_launch_dependents();
-    const int r = blockIdx.x, unit = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int s = r / a.seq_len, i = r - s * a.seq_len;
+    const int unit = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int groups = (a.seq_len + rows_per_block - 1) / rows_per_block;
+    const int s = blockIdx.x / groups, i0 = (blockIdx.x - s * groups) * rows_per_block;
+    const int i1 = i0 + rows_per_block < a.seq_len ? i0 + rows_per_block : a.seq_len;
+    for (int i = i0; i < i1; ++i) {
+    const int r = s * a.seq_len + i;
+    __syncthreads();                               // y and red are free again
     const int p = (a.pos ? a.pos[s] : a.pos0) + i;
     const int D = a.dim, V = a.vdim, G = a.kv_heads, H = a.heads;
     const int qk = G * D, C = 2 * qk + H * V, taps = a.taps;
@@ -54,7 +59,7 @@ __global__ void __launch_bounds__(128) delta_prep_kernel(b200_delta_args a) {
     if (unit >= G) {                               // a value head
         const int h = unit - G;
         for (int d = tid; d < V; d += 128) out[2 * qk + h * V + d] = conv(2 * qk + h * V + d);
-        return;
+        continue;
     }
     const int g = unit;
     float sq = 0.f, sk = 0.f;
@@ -84,10 +89,11 @@ __global__ void __launch_bounds__(128) delta_prep_kernel(b200_delta_args a) {
         out[qk + g * D + d] = y[D + d] * fk;
     }
     if (tid == 0) out[C + 2 * H + g] = dot * fq * fk;
+    }
 }
 
 // ------------------------------------------------------------------ rule
-constexpr int kDeltaBatch = 16;      // tokens staged in shared memory at a time (two buffers)
+constexpr int kDeltaBatch = 16;      // most tokens staged in shared memory at a time (two buffers)
 
 __device__ __forceinline__ void cp_async4(void* dst, const void* src) {
     asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(smem_u32(dst)), "l"(src) : "memory");
@@ -104,7 +110,7 @@ __device__ __forceinline__ void cp_wait() { asm volatile("cp.async.wait_group %0
 // ([head][column][row]) so that a lane's rows are contiguous.  Tokens are staged 16 at a time by cp.async into one of
 // two buffers while the other one is being consumed.
 template <int NR, int SL>
-__global__ void __launch_bounds__(256) delta_rule_kernel(b200_delta_args a, int vec) {
+__global__ void __launch_bounds__(256) delta_rule_kernel(b200_delta_args a, int vec, int tb) {
     extern __shared__ __align__(16) float sm[];
     pdl_wait_prior_grid();
     pdl_launch_dependents();
@@ -128,14 +134,14 @@ __global__ void __launch_bounds__(256) delta_rule_kernel(b200_delta_args a, int 
             S[n] = (p0 > 0 && col && i < D) ? src[i] : 0.f;
         }
     }
-    for (int e = tid; e < 2 * kDeltaBatch * STRIDE; e += 256) sm[e] = 0.f;      // rows beyond dim stay zero
+    for (int e = tid; e < 2 * tb * STRIDE; e += 256) sm[e] = 0.f;               // rows beyond dim stay zero
     __syncthreads();
     const int tok = tid >> 4, sub = tid & 15;        // 16 threads stage one token
     auto stage = [&](int buf, int t0) {
-        const int nb = a.seq_len - t0 < kDeltaBatch ? a.seq_len - t0 : kDeltaBatch;
+        const int nb = a.seq_len - t0 < tb ? a.seq_len - t0 : tb;
         if (tok < nb) {
             const float* w = a.work + (size_t)(s * a.seq_len + t0 + tok) * a.ldw;
-            float* dst = sm + (buf * kDeltaBatch + tok) * STRIDE;
+            float* dst = sm + (buf * tb + tok) * STRIDE;
             if (vec) {
                 for (int c = sub * 4; c < D; c += 64) {
                     cp_async16f(dst + c, w + qk + g * D + c);
@@ -157,19 +163,19 @@ __global__ void __launch_bounds__(256) delta_rule_kernel(b200_delta_args a, int 
     };
     stage(0, 0);
     int buf = 0;
-    for (int t0 = 0; t0 < a.seq_len; t0 += kDeltaBatch, buf ^= 1) {
-        const int nb = a.seq_len - t0 < kDeltaBatch ? a.seq_len - t0 : kDeltaBatch;
-        if (t0 + kDeltaBatch < a.seq_len) {
-            stage(buf ^ 1, t0 + kDeltaBatch);
+    for (int t0 = 0; t0 < a.seq_len; t0 += tb, buf ^= 1) {
+        const int nb = a.seq_len - t0 < tb ? a.seq_len - t0 : tb;
+        if (t0 + tb < a.seq_len) {
+            stage(buf ^ 1, t0 + tb);
             cp_wait<1>();
         } else {
             cp_wait<0>();
         }
         __syncthreads();
         for (int b = 0; b < nb; ++b) {
-            const float* kk = sm + (buf * kDeltaBatch + b) * STRIDE + slice * NR;
+            const float* kk = sm + (buf * tb + b) * STRIDE + slice * NR;
             const float* qq = kk + Dp;
-            const float* sc = sm + (buf * kDeltaBatch + b) * STRIDE + 2 * Dp;
+            const float* sc = sm + (buf * tb + b) * STRIDE + 2 * Dp;
             float kr[NR];
             float dk0 = 0.f, dk1 = 0.f, dq0 = 0.f, dq1 = 0.f;
 #pragma unroll
@@ -186,17 +192,20 @@ __global__ void __launch_bounds__(256) delta_rule_kernel(b200_delta_args a, int 
                 dq0 = fmaf(S[n + 2], q4.z, dq0);
                 dq1 = fmaf(S[n + 3], q4.w, dq1);
             }
-            float dk = dk0 + dk1, dq = dq0 + dq1;
+            // both sums in one butterfly: after the first exchange the even lanes carry S^T k, the odd lanes S^T q
+            // (shuffles and shared-memory reads are what this loop is bound by)
+            const float dk = dk0 + dk1, dq = dq0 + dq1;
+            float mine = (lane & 1) ? dq : dk;
+            mine += __shfl_xor_sync(0xffffffffu, (lane & 1) ? dk : dq, 1);
 #pragma unroll
-            for (int o = 1; o < SL; o <<= 1) {
-                dk += __shfl_xor_sync(0xffffffffu, dk, o);
-                dq += __shfl_xor_sync(0xffffffffu, dq, o);
-            }
-            const float vj = sc[cw], beta = sc[COLS], dec = sc[COLS + 1], kq = sc[COLS + 2];
-            const float u = beta * (vj - dec * dk);
+            for (int o = 2; o < SL; o <<= 1) mine += __shfl_xor_sync(0xffffffffu, mine, o);
+            const float dkt = __shfl_sync(0xffffffffu, mine, lane & ~(SL - 1));
+            const float vj = sc[cw];
+            const float4 par = *reinterpret_cast<const float4*>(sc + COLS);      // beta, decay, k.q
+            const float u = par.x * (vj - par.y * dkt);
 #pragma unroll
-            for (int n = 0; n < NR; ++n) S[n] = fmaf(kr[n], u, dec * S[n]);
-            if (slice == 0 && col) a.o[(size_t)(s * a.seq_len + t0 + b) * a.ldo + (size_t)h * V + j] = fmaf(u, kq, dec * dq);
+            for (int n = 0; n < NR; ++n) S[n] = fmaf(kr[n], u, par.y * S[n]);
+            if (slice == 1 && col) a.o[(size_t)(s * a.seq_len + t0 + b) * a.ldo + (size_t)h * V + j] = fmaf(u, par.z, par.y * mine);
         }
         __syncthreads();                           // the buffer is free for the copies after the next ones
     }
@@ -222,13 +231,14 @@ __global__ void __launch_bounds__(256) delta_rule_kernel(b200_delta_args a, int 
 template <int NR, int SL>
 static int launch_delta_rule(const b200_delta_args* a, cudaStream_t s) {
     constexpr int COLS = 256 / SL;
-    const size_t smem = (size_t)2 * kDeltaBatch * (2 * NR * SL + COLS + 4) * sizeof(float);
+    const int tb = a->seq_len < kDeltaBatch ? a->seq_len : kDeltaBatch;      // (a decode step stages one token)
+    const size_t smem = (size_t)2 * tb * (2 * NR * SL + COLS + 4) * sizeof(float);
     if (smem > 48 * 1024)
         B200_CUDA_CHECK(cudaFuncSetAttribute(delta_rule_kernel<NR, SL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     const int qk = a->kv_heads * a->dim;
     const int vec = (a->dim % 4 == 0 && a->ldw % 4 == 0 && qk % 4 == 0 && (reinterpret_cast<uintptr_t>(a->work) & 15) == 0) ? 1 : 0;
     dim3 grid(a->n_seq, a->heads, (a->vdim + COLS - 1) / COLS);
-    B200_CUDA_CHECK(launch(delta_rule_kernel<NR, SL>, grid, dim3(256), smem, s, a->pdl != 0, *a, vec));
+    B200_CUDA_CHECK(launch(delta_rule_kernel<NR, SL>, grid, dim3(256), smem, s, a->pdl != 0, *a, vec, tb));
     return B200_OK;
 }
 
@@ -251,8 +261,9 @@ extern "C" int b200_delta_prep(const b200_delta_args* a, void* stream) {
     if (!a->conv_w || !a->A_log || !a->dt_bias) return fail(B200_EINVAL, "b200_delta_prep: parameters missing");
     const size_t smem = (size_t)(2 * a->dim > a->vdim ? 2 * a->dim : a->vdim) * sizeof(float);
     if (smem > 48 * 1024) return fail(B200_ELIMIT, "b200_delta_prep: dim %d exceeds shared memory", a->dim);
-    B200_CUDA_CHECK(launch(delta_prep_kernel, dim3(a->n_seq * a->seq_len, a->kv_heads + a->heads), dim3(128), smem,
-                           static_cast<cudaStream_t>(stream), a->pdl != 0, *a));
+    const int rpb = a->seq_len >= 64 ? 8 : 1;
+    B200_CUDA_CHECK(launch(delta_prep_kernel, dim3(a->n_seq * ((a->seq_len + rpb - 1) / rpb), a->kv_heads + a->heads), dim3(128),
+                           smem, static_cast<cudaStream_t>(stream), a->pdl != 0, *a, rpb));
     return B200_OK;
 }
 
@@ -260,9 +271,10 @@ extern "C" int b200_delta_rule(const b200_delta_args* a, void* stream) {
     if (int rc = check_delta(a, "b200_delta_rule")) return rc;
     if (!a->o) return fail(B200_EINVAL, "b200_delta_rule: o missing");
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    if (a->dim <= 64) return launch_delta_rule<8, 8>(a, s);
-    if (a->dim <= 128) return launch_delta_rule<8, 16>(a, s);
-    if (a->dim <= 256) return launch_delta_rule<16, 16>(a, s);
-    if (a->dim <= 512) return launch_delta_rule<32, 16>(a, s);
+    // (few rows per lane: the work of a token is a chain of dependent steps, so the more warps share it the better)
+    if (a->dim <= 64) return launch_delta_rule<4, 16>(a, s);
+    if (a->dim <= 128) return launch_delta_rule<4, 32>(a, s);
+    if (a->dim <= 256) return launch_delta_rule<8, 32>(a, s);
+    if (a->dim <= 512) return launch_delta_rule<16, 32>(a, s);
     return fail(B200_ELIMIT, "b200_delta_rule: dim %d > 512", a->dim);
 }

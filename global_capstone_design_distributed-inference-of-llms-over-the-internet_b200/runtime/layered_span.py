@@ -380,7 +380,7 @@ class LayeredSpan(NativeSpan):
         the sessions' capacity only, so a captured step keeps it."""
         if T > MAX_DECODE_BATCH:
             return 1, None
-        splits = max(1, min(ATTN_MAX_SPLITS, self.kv_capacity // 128, (4 * 148) // (T * m.heads)))
+        splits = max(1, min(ATTN_MAX_SPLITS, self.kv_capacity // 128, (16 * 148) // (T * m.heads)))
         return (splits, self.attn_part) if splits > 1 else (1, None)
 
     def _mixer_sink_attention(self, T: int, P: dict, where: dict, proj: torch.Tensor, cat: torch.Tensor) -> None:
