@@ -42,10 +42,18 @@ __global__ void __launch_bounds__(128) delta_prep_kernel(b200_delta_args a, int 
     auto conv = [&](int c) {
         const float* w = a.conv_w + (size_t)c * taps;
         float acc = 0.f;
-        for (int b = taps - 1; b >= 0; --b) {      // oldest input first
-            if (p - b < 0) continue;               // before the sequence's start: zero
-            const float x = b <= i ? row[c - (ptrdiff_t)b * a.ldp] : ring[(size_t)((p - b) % taps) * C + c];
-            acc = fmaf(w[taps - 1 - b], x, acc);
+        if (i >= taps - 1) {                       // every input is a row of this launch (all but its first rows)
+            for (int b = taps - 1; b >= 0; --b) acc = fmaf(w[taps - 1 - b], row[c - (ptrdiff_t)b * a.ldp], acc);
+        } else {
+            for (int b = taps - 1; b >= 0; --b) {  // oldest input first
+                if (p - b < 0) continue;           // before the sequence's start: zero
+                float x;
+                if (b <= i)
+                    x = row[c - (ptrdiff_t)b * a.ldp];
+                else
+                    x = ring[(size_t)((p - b) % taps) * C + c];
+                acc = fmaf(w[taps - 1 - b], x, acc);
+            }
         }
         return acc / (1.0f + expf(-acc));
     };

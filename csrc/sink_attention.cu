@@ -132,6 +132,8 @@ __global__ void __launch_bounds__(kSinkWarps * 32) sink_attn_kernel(b200_sink_at
     const char* vb = sink_plane(a, t, 1);
     const size_t re = (size_t)a.row_elems;
     const bool vec16 = !f32 && D % 8 == 0 && a.row_elems % 8 == 0 && (reinterpret_cast<uintptr_t>(kb) & 15) == 0;
+    // value columns of a lane: lane + 32 i, or (16-bit caches, even sizes) the pairs 64 i + 2 lane, + 1
+    const bool pair = !f32 && NPER % 2 == 0 && V % 2 == 0 && a.row_elems % 2 == 0 && (reinterpret_cast<uintptr_t>(vb) & 3) == 0;
     const bool sink_here = warp == 0 && z == 0 && a.sink > 0.f;
     float m = sink_here ? 0.f : -INFINITY, l = sink_here ? a.sink : 0.f, acc[NPER];
 #pragma unroll
@@ -144,11 +146,11 @@ __global__ void __launch_bounds__(kSinkWarps * 32) sink_attn_kernel(b200_sink_at
             // of key L, which pass L / 4 computed in subgroup L % 4
             const int part = lane & 7, sg = lane >> 3;
             const uint16_t* kbase = reinterpret_cast<const uint16_t*>(kb) + (size_t)g * D;
-#pragma unroll 2
-            for (int it = 0; it < 8; ++it) {
-                const int jj = it * 4 + sg;
+#pragma unroll
+            for (int it = 0; it < 8; ++it) {          // (unrolled: the passes' loads are all in flight together)
+                const int jj = it * 4 + sg < n ? it * 4 + sg : n - 1;     // (beyond the chunk: a valid row, result unused)
                 float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;
-                if (jj < n) {
+                {
                     const uint16_t* kr = kbase + (size_t)(j0 + jj) * re;
                     for (int c = part * 8; c < D; c += 64) {
                         const uint4 v = *reinterpret_cast<const uint4*>(kr + c);
@@ -209,16 +211,32 @@ __global__ void __launch_bounds__(kSinkWarps * 32) sink_attn_kernel(b200_sink_at
         m = mn;
 #pragma unroll
         for (int i = 0; i < NPER; ++i) acc[i] *= alpha;
-        for (int j = 0; j < n; ++j) {
-            const float w = __shfl_sync(0xffffffffu, pj, j);
-            const size_t base = (size_t)(j0 + j) * re + (size_t)g * V;
+        if (pair) {          // two neighbouring 16-bit values per lane and load: 128 contiguous bytes per warp
+            const uint16_t* vrow = reinterpret_cast<const uint16_t*>(vb) + (size_t)j0 * re + (size_t)g * V + 2 * lane;
+#pragma unroll 8
+            for (int j = 0; j < n; ++j) {
+                const float w = __shfl_sync(0xffffffffu, pj, j);
 #pragma unroll
-            for (int i = 0; i < NPER; ++i) {
-                const int d = lane + 32 * i;
-                if (d < V) {
-                    const float v = f32 ? reinterpret_cast<const float*>(vb)[base + d]
-                                        : h16_to_float(reinterpret_cast<const uint16_t*>(vb)[base + d], bf);
-                    acc[i] = fmaf(w, v, acc[i]);
+                for (int i = 0; i < NPER / 2; ++i) {
+                    if (64 * i + 2 * lane < V) {
+                        const uint32_t x = *reinterpret_cast<const uint32_t*>(vrow + (size_t)j * re + 64 * i);
+                        acc[2 * i] = fmaf(w, h16_to_float((uint16_t)(x & 0xffff), bf), acc[2 * i]);
+                        acc[2 * i + 1] = fmaf(w, h16_to_float((uint16_t)(x >> 16), bf), acc[2 * i + 1]);
+                    }
+                }
+            }
+        } else {
+            for (int j = 0; j < n; ++j) {
+                const float w = __shfl_sync(0xffffffffu, pj, j);
+                const size_t base = (size_t)(j0 + j) * re + (size_t)g * V;
+#pragma unroll
+                for (int i = 0; i < NPER; ++i) {
+                    const int d = lane + 32 * i;
+                    if (d < V) {
+                        const float v = f32 ? reinterpret_cast<const float*>(vb)[base + d]
+                                            : h16_to_float(reinterpret_cast<const uint16_t*>(vb)[base + d], bf);
+                        acc[i] = fmaf(w, v, acc[i]);
+                    }
                 }
             }
         }
@@ -227,7 +245,7 @@ __global__ void __launch_bounds__(kSinkWarps * 32) sink_attn_kernel(b200_sink_at
     float* mine = ws + warp * (V + 2);
 #pragma unroll
     for (int i = 0; i < NPER; ++i) {
-        const int d = lane + 32 * i;
+        const int d = pair ? 64 * (i / 2) + 2 * lane + (i & 1) : lane + 32 * i;
         if (d < V) mine[d] = acc[i];
     }
     if (lane == 0) {
