@@ -134,10 +134,18 @@ __global__ void __launch_bounds__(kSinkWarps * 32) sink_attn_kernel(b200_sink_at
     const bool vec16 = !f32 && D % 8 == 0 && a.row_elems % 8 == 0 && (reinterpret_cast<uintptr_t>(kb) & 15) == 0;
     // value columns of a lane: lane + 32 i, or (16-bit caches, even sizes) the pairs 64 i + 2 lane, + 1
     const bool pair = !f32 && NPER % 2 == 0 && V % 2 == 0 && a.row_elems % 2 == 0 && (reinterpret_cast<uintptr_t>(vb) & 3) == 0;
+    // ... or (sizes and addresses that allow 16-byte loads) 8 lanes per key with 8 neighbouring columns each, four keys
+    // per pass: the lanes of a subgroup sum over their keys, the subgroups meet at the end
+    const bool vecv = vec16 && NPER % 2 == 0 && V % 8 == 0 && (reinterpret_cast<uintptr_t>(vb) & 15) == 0;
     const bool sink_here = warp == 0 && z == 0 && a.sink > 0.f;
     float m = sink_here ? 0.f : -INFINITY, l = sink_here ? a.sink : 0.f, acc[NPER];
+    float accv[NPER / 2 > 0 ? NPER / 2 : 1][8];
 #pragma unroll
     for (int i = 0; i < NPER; ++i) acc[i] = 0.f;
+#pragma unroll
+    for (int i = 0; i < (NPER / 2 > 0 ? NPER / 2 : 1); ++i)
+#pragma unroll
+        for (int e = 0; e < 8; ++e) accv[i][e] = 0.f;
     for (int j0 = lo + warp * 32; j0 <= hi; j0 += kSinkWarps * 32) {
         const int n = hi - j0 + 1 < 32 ? hi - j0 + 1 : 32;
         float s = -INFINITY;
@@ -211,7 +219,34 @@ __global__ void __launch_bounds__(kSinkWarps * 32) sink_attn_kernel(b200_sink_at
         m = mn;
 #pragma unroll
         for (int i = 0; i < NPER; ++i) acc[i] *= alpha;
-        if (pair) {          // two neighbouring 16-bit values per lane and load: 128 contiguous bytes per warp
+        if (vecv) {
+            const int part = lane & 7, sg = lane >> 3;
+            const uint16_t* vbase = reinterpret_cast<const uint16_t*>(vb) + (size_t)g * V + part * 8;
+#pragma unroll
+            for (int i = 0; i < NPER / 2; ++i)
+#pragma unroll
+                for (int e = 0; e < 8; ++e) accv[i][e] *= alpha;
+#pragma unroll
+            for (int it = 0; it < 8; ++it) {
+                const int jj = it * 4 + sg, jc = jj < n ? jj : n - 1;
+                const float wj = __shfl_sync(0xffffffffu, pj, jc);
+                const float w = jj < n ? wj : 0.f;
+#pragma unroll
+                for (int i = 0; i < NPER / 2; ++i) {
+                    if (64 * i + part * 8 < V) {
+                        const uint4 x = *reinterpret_cast<const uint4*>(vbase + (size_t)(j0 + jc) * re + 64 * i);
+                        accv[i][0] = fmaf(w, h16_to_float((uint16_t)(x.x & 0xffff), bf), accv[i][0]);
+                        accv[i][1] = fmaf(w, h16_to_float((uint16_t)(x.x >> 16), bf), accv[i][1]);
+                        accv[i][2] = fmaf(w, h16_to_float((uint16_t)(x.y & 0xffff), bf), accv[i][2]);
+                        accv[i][3] = fmaf(w, h16_to_float((uint16_t)(x.y >> 16), bf), accv[i][3]);
+                        accv[i][4] = fmaf(w, h16_to_float((uint16_t)(x.z & 0xffff), bf), accv[i][4]);
+                        accv[i][5] = fmaf(w, h16_to_float((uint16_t)(x.z >> 16), bf), accv[i][5]);
+                        accv[i][6] = fmaf(w, h16_to_float((uint16_t)(x.w & 0xffff), bf), accv[i][6]);
+                        accv[i][7] = fmaf(w, h16_to_float((uint16_t)(x.w >> 16), bf), accv[i][7]);
+                    }
+                }
+            }
+        } else if (pair) {   // two neighbouring 16-bit values per lane and load: 128 contiguous bytes per warp
             const uint16_t* vrow = reinterpret_cast<const uint16_t*>(vb) + (size_t)j0 * re + (size_t)g * V + 2 * lane;
 #pragma unroll 8
             for (int j = 0; j < n; ++j) {
@@ -243,10 +278,24 @@ __global__ void __launch_bounds__(kSinkWarps * 32) sink_attn_kernel(b200_sink_at
     }
     // the warps' shares meet in warp order
     float* mine = ws + warp * (V + 2);
+    if (vecv) {
 #pragma unroll
-    for (int i = 0; i < NPER; ++i) {
-        const int d = pair ? 64 * (i / 2) + 2 * lane + (i & 1) : lane + 32 * i;
-        if (d < V) mine[d] = acc[i];
+        for (int i = 0; i < NPER / 2; ++i) {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                float v = accv[i][e];
+                v += __shfl_xor_sync(0xffffffffu, v, 8);
+                v += __shfl_xor_sync(0xffffffffu, v, 16);
+                const int d = 64 * i + (lane & 7) * 8 + e;
+                if (lane < 8 && d < V) mine[d] = v;
+            }
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < NPER; ++i) {
+            const int d = pair ? 64 * (i / 2) + 2 * lane + (i & 1) : lane + 32 * i;
+            if (d < V) mine[d] = acc[i];
+        }
     }
     if (lane == 0) {
         mine[V] = m;

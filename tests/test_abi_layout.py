@@ -23,6 +23,11 @@ int main(void) {
     printf("attn %zu %zu %zu %zu\n", sizeof(b200_attn_decode_args), offsetof(b200_attn_decode_args, scale),
            offsetof(b200_attn_decode_args, ll_scratch), offsetof(b200_attn_decode_args, chain));
     printf("hop %zu %zu %zu\n", sizeof(b200_hop_args), offsetof(b200_hop_args, counter), offsetof(b200_hop_args, pdl));
+    printf("addnorm %zu %zu %zu\n", sizeof(b200_add_norm_args), offsetof(b200_add_norm_args, eps), offsetof(b200_add_norm_args, add_scale));
+    printf("sink %zu %zu %zu %zu %zu\n", sizeof(b200_sink_attn_args), offsetof(b200_sink_attn_args, bias),
+           offsetof(b200_sink_attn_args, k_cache), offsetof(b200_sink_attn_args, T), offsetof(b200_sink_attn_args, out));
+    printf("delta %zu %zu %zu %zu %zu\n", sizeof(b200_delta_args), offsetof(b200_delta_args, conv_w),
+           offsetof(b200_delta_args, state_off), offsetof(b200_delta_args, n_seq), offsetof(b200_delta_args, o));
     return 0;
 }
 """
@@ -30,7 +35,7 @@ int main(void) {
 
 @pytest.mark.skipif(shutil.which("gcc") is None, reason="needs a host C compiler")
 def test_ctypes_structs_match_the_header(tmp_path):
-    from petals_b200.ops._prototypes import AttnDecodeArgs, HopArgs
+    from petals_b200.ops._prototypes import AddNormArgs, AttnDecodeArgs, DeltaArgs, HopArgs, SinkAttnArgs
     from petals_b200.ops.native import GemmArgs, LLChainArgs
     from petals_b200.parallel.tensor_parallel import TpArgs
 
@@ -47,6 +52,11 @@ def test_ctypes_structs_match_the_header(tmp_path):
     assert out["attn"] == [ctypes.sizeof(AttnDecodeArgs), AttnDecodeArgs.scale.offset, AttnDecodeArgs.ll_scratch.offset,
                            AttnDecodeArgs.chain.offset]
     assert out["hop"] == [ctypes.sizeof(HopArgs), HopArgs.counter.offset, HopArgs.pdl.offset]
+    assert out["addnorm"] == [ctypes.sizeof(AddNormArgs), AddNormArgs.eps.offset, AddNormArgs.add_scale.offset]
+    assert out["sink"] == [ctypes.sizeof(SinkAttnArgs), SinkAttnArgs.bias.offset, SinkAttnArgs.k_cache.offset,
+                           SinkAttnArgs.T.offset, SinkAttnArgs.out.offset]
+    assert out["delta"] == [ctypes.sizeof(DeltaArgs), DeltaArgs.conv_w.offset, DeltaArgs.state_off.offset,
+                            DeltaArgs.n_seq.offset, DeltaArgs.o.offset]
 
 
 def test_library_loads_with_every_symbol_resolved():
