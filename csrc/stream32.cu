@@ -47,14 +47,54 @@ __global__ void __launch_bounds__(128) embed_pos_f32_kernel(const long long* __r
 
 // ------------------------------------------------------------------ residual update + RMS norm
 // One block per token.  The updated row is kept in shared memory between the two passes.
-__global__ void __launch_bounds__(256) add_rms_norm_kernel(b200_add_norm_args a) {
-    extern __shared__ float row[];
+__global__ void __launch_bounds__(256) add_rms_norm_kernel(b200_add_norm_args a, int vec) {
+    extern __shared__ __align__(16) float row[];
     __shared__ float red[8];
     pdl_wait_prior_grid();
     pdl_launch_dependents();
     const int t = blockIdx.x;
     float* x = a.x + (size_t)t * a.ldx;
     float ss = 0.f;
+    if (vec) {      // four columns per thread and pass (16-byte accesses); the sums keep their order per column
+        for (int c = threadIdx.x * 4; c < a.width; c += blockDim.x * 4) {
+            float4 v = *reinterpret_cast<const float4*>(x + c);
+            float4 add = make_float4(0.f, 0.f, 0.f, 0.f);
+            bool any = false;
+            if (a.add_a) {
+                const float4 y = *reinterpret_cast<const float4*>(a.add_a + (size_t)t * a.lda + c);
+                add.x += y.x, add.y += y.y, add.z += y.z, add.w += y.w;
+                any = true;
+            }
+            if (a.add_b) {
+                const float4 y = *reinterpret_cast<const float4*>(a.add_b + (size_t)t * a.ldb + c);
+                add.x += y.x, add.y += y.y, add.z += y.z, add.w += y.w;
+                any = true;
+            }
+            if (a.pair_y) {
+                float4 m = make_float4(0.f, 0.f, 0.f, 0.f);
+                for (int k = 0; k < a.top; ++k) {
+                    const size_t p = (size_t)t * a.top + k;
+                    const float4 y = *reinterpret_cast<const float4*>(a.pair_y + p * a.ldp + c);
+                    const float w = a.pair_w ? a.pair_w[p] : 1.0f;
+                    if (a.pair_w)
+                        m.x += w * y.x, m.y += w * y.y, m.z += w * y.z, m.w += w * y.w;
+                    else
+                        m.x += y.x, m.y += y.y, m.z += y.z, m.w += y.w;
+                }
+                add.x += m.x, add.y += m.y, add.z += m.z, add.w += m.w;
+                any = true;
+            }
+            if (any) {
+                v.x += a.add_scale * add.x, v.y += a.add_scale * add.y, v.z += a.add_scale * add.z, v.w += a.add_scale * add.w;
+                *reinterpret_cast<float4*>(x + c) = v;
+            }
+            *reinterpret_cast<float4*>(row + c) = v;
+            ss += v.x * v.x;
+            ss += v.y * v.y;
+            ss += v.z * v.z;
+            ss += v.w * v.w;
+        }
+    } else
     for (int c = threadIdx.x; c < a.width; c += blockDim.x) {
         float v = x[c];
         float add = 0.f;
@@ -87,6 +127,18 @@ __global__ void __launch_bounds__(256) add_rms_norm_kernel(b200_add_norm_args a)
 #pragma unroll
     for (int w = 0; w < 8; ++w) tot += red[w];
     const float rstd = 1.0f / sqrtf(tot / (float)a.width + a.eps);
+    if (vec && a.out_dtype != B200_F32) {
+        const int bf = a.out_dtype == B200_BF16;
+        for (int c = threadIdx.x * 4; c < a.width; c += blockDim.x * 4) {
+            const float4 v = *reinterpret_cast<const float4*>(row + c);
+            const float4 g = *reinterpret_cast<const float4*>(a.gain + c);
+            uint2 o;
+            o.x = (uint32_t)float_to_h16(v.x * rstd * (a.gain_offset + g.x), bf) | ((uint32_t)float_to_h16(v.y * rstd * (a.gain_offset + g.y), bf) << 16);
+            o.y = (uint32_t)float_to_h16(v.z * rstd * (a.gain_offset + g.z), bf) | ((uint32_t)float_to_h16(v.w * rstd * (a.gain_offset + g.w), bf) << 16);
+            *reinterpret_cast<uint2*>(static_cast<uint16_t*>(a.out) + (size_t)t * a.ldo + c) = o;
+        }
+        return;
+    }
     for (int c = threadIdx.x; c < a.width; c += blockDim.x)
         store_elem(a.out, (size_t)t * a.ldo + c, row[c] * rstd * (a.gain_offset + a.gain[c]), a.out_dtype);
 }
@@ -222,7 +274,11 @@ extern "C" int b200_add_rms_norm(const b200_add_norm_args* a, void* stream) {
     if (smem > 200 * 1024) return fail(B200_ELIMIT, "b200_add_rms_norm: width %d exceeds the row buffer", a->width);
     if (smem > 48 * 1024)
         B200_CUDA_CHECK(cudaFuncSetAttribute(add_rms_norm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    B200_CUDA_CHECK(launch(add_rms_norm_kernel, dim3(a->T), dim3(256), smem, static_cast<cudaStream_t>(stream), a->pdl != 0, *a));
+    auto al16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+    const int vec = (a->width % 4 == 0 && a->ldx % 4 == 0 && al16(a->x) && (!a->add_a || (a->lda % 4 == 0 && al16(a->add_a))) &&
+                     (!a->add_b || (a->ldb % 4 == 0 && al16(a->add_b))) && (!a->pair_y || (a->ldp % 4 == 0 && al16(a->pair_y))) &&
+                     (!a->out || (al16(a->gain) && a->ldo % 4 == 0 && (reinterpret_cast<uintptr_t>(a->out) & 7) == 0))) ? 1 : 0;
+    B200_CUDA_CHECK(launch(add_rms_norm_kernel, dim3(a->T), dim3(256), smem, static_cast<cudaStream_t>(stream), a->pdl != 0, *a, vec));
     return B200_OK;
 }
 
