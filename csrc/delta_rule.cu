@@ -113,33 +113,34 @@ __device__ __forceinline__ void cp_commit() { asm volatile("cp.async.commit_grou
 template <int N>
 __device__ __forceinline__ void cp_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory"); }
 
-// Block = (sequence, head, 256 / SL columns of S).  Lane = column * SL + slice: column j's rows slice * NR .. + NR are in
-// the registers of one lane, the dot products over a column meet by log2(SL) shuffles.  The state is kept column-major
-// ([head][column][row]) so that a lane's rows are contiguous.  Tokens are staged 16 at a time by cp.async into one of
-// two buffers while the other one is being consumed.
-template <int NR, int SL>
+// Block = (sequence, head, NC * 256 / SL columns of S).  A group of SL lanes holds NC columns: column j's rows
+// slice * NR .. + NR are in the registers of one lane, the dot products over a column meet by log2(SL) shuffles.  The
+// NC columns of a group share every read of k and q and give the warp NC independent chains per token.  The state is
+// kept column-major ([head][column][row]) so that a lane's rows are contiguous.  Tokens are staged 16 at a time by
+// cp.async into one of two buffers while the other one is being consumed.
+template <int NR, int SL, int NC>
 __global__ void __launch_bounds__(256) delta_rule_kernel(b200_delta_args a, int vec, int tb) {
     extern __shared__ __align__(16) float sm[];
     pdl_wait_prior_grid();
     pdl_launch_dependents();
-    constexpr int Dp = NR * SL, COLS = 256 / SL, CPW = 32 / SL;
+    constexpr int Dp = NR * SL, COLS = NC * 256 / SL, CPW = 32 / SL;
     constexpr int STRIDE = 2 * Dp + COLS + 4;       // k | q | v columns | beta, decay, k.q, -
     const int s = blockIdx.x, h = blockIdx.y, tile = blockIdx.z;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int slice = lane % SL, cw = warp * CPW + lane / SL, j = tile * COLS + cw;
+    const int slice = lane % SL, cw = (warp * CPW + lane / SL) * NC, j = tile * COLS + cw;    // first column of the group
     const int D = a.dim, V = a.vdim, H = a.heads;
     const int g = h / (H / a.kv_heads);
     const int qk = a.kv_heads * D, C = 2 * qk + H * V;
     const int p0 = a.pos ? a.pos[s] : a.pos0;
-    const bool col = j < V;
     float* st = delta_state(a, s);
-    float S[NR];
-    {
-        const float* src = st + (((size_t)(p0 & 1) * H + h) * V + j) * D;
+    float S[NC][NR];
+#pragma unroll
+    for (int c = 0; c < NC; ++c) {
+        const float* src = st + (((size_t)(p0 & 1) * H + h) * V + j + c) * D;
 #pragma unroll
         for (int n = 0; n < NR; ++n) {
             const int i = slice * NR + n;
-            S[n] = (p0 > 0 && col && i < D) ? src[i] : 0.f;
+            S[c][n] = (p0 > 0 && j + c < V && i < D) ? src[i] : 0.f;
         }
     }
     for (int e = tid; e < 2 * tb * STRIDE; e += 256) sm[e] = 0.f;               // rows beyond dim stay zero
@@ -185,44 +186,60 @@ __global__ void __launch_bounds__(256) delta_rule_kernel(b200_delta_args a, int 
             const float* qq = kk + Dp;
             const float* sc = sm + (buf * tb + b) * STRIDE + 2 * Dp;
             float kr[NR];
-            float dk0 = 0.f, dk1 = 0.f, dq0 = 0.f, dq1 = 0.f;
+            float dk[NC], dq[NC];
+#pragma unroll
+            for (int c = 0; c < NC; ++c) dk[c] = dq[c] = 0.f;
 #pragma unroll
             for (int n = 0; n < NR; n += 4) {
                 const float4 k4 = *reinterpret_cast<const float4*>(kk + n);
                 const float4 q4 = *reinterpret_cast<const float4*>(qq + n);
                 kr[n] = k4.x, kr[n + 1] = k4.y, kr[n + 2] = k4.z, kr[n + 3] = k4.w;
-                dk0 = fmaf(S[n], k4.x, dk0);
-                dk1 = fmaf(S[n + 1], k4.y, dk1);
-                dk0 = fmaf(S[n + 2], k4.z, dk0);
-                dk1 = fmaf(S[n + 3], k4.w, dk1);
-                dq0 = fmaf(S[n], q4.x, dq0);
-                dq1 = fmaf(S[n + 1], q4.y, dq1);
-                dq0 = fmaf(S[n + 2], q4.z, dq0);
-                dq1 = fmaf(S[n + 3], q4.w, dq1);
+#pragma unroll
+                for (int c = 0; c < NC; ++c) {
+                    dk[c] = fmaf(S[c][n], k4.x, dk[c]);
+                    dq[c] = fmaf(S[c][n], q4.x, dq[c]);
+                    dk[c] = fmaf(S[c][n + 1], k4.y, dk[c]);
+                    dq[c] = fmaf(S[c][n + 1], q4.y, dq[c]);
+                    dk[c] = fmaf(S[c][n + 2], k4.z, dk[c]);
+                    dq[c] = fmaf(S[c][n + 2], q4.z, dq[c]);
+                    dk[c] = fmaf(S[c][n + 3], k4.w, dk[c]);
+                    dq[c] = fmaf(S[c][n + 3], q4.w, dq[c]);
+                }
             }
-            // both sums in one butterfly: after the first exchange the even lanes carry S^T k, the odd lanes S^T q
-            // (shuffles and shared-memory reads are what this loop is bound by)
-            const float dk = dk0 + dk1, dq = dq0 + dq1;
-            float mine = (lane & 1) ? dq : dk;
-            mine += __shfl_xor_sync(0xffffffffu, (lane & 1) ? dk : dq, 1);
+            // both sums of a column in one butterfly: after the first exchange the even lanes carry S^T k, the odd
+            // lanes S^T q (shuffles and shared-memory reads are what this loop is bound by)
+            float mine[NC];
 #pragma unroll
-            for (int o = 2; o < SL; o <<= 1) mine += __shfl_xor_sync(0xffffffffu, mine, o);
-            const float dkt = __shfl_sync(0xffffffffu, mine, lane & ~(SL - 1));
-            const float vj = sc[cw];
+            for (int c = 0; c < NC; ++c) {
+                mine[c] = (lane & 1) ? dq[c] : dk[c];
+                mine[c] += __shfl_xor_sync(0xffffffffu, (lane & 1) ? dk[c] : dq[c], 1);
+            }
+#pragma unroll
+            for (int o = 2; o < SL; o <<= 1) {
+#pragma unroll
+                for (int c = 0; c < NC; ++c) mine[c] += __shfl_xor_sync(0xffffffffu, mine[c], o);
+            }
             const float4 par = *reinterpret_cast<const float4*>(sc + COLS);      // beta, decay, k.q
-            const float u = par.x * (vj - par.y * dkt);
 #pragma unroll
-            for (int n = 0; n < NR; ++n) S[n] = fmaf(kr[n], u, par.y * S[n]);
-            if (slice == 1 && col) a.o[(size_t)(s * a.seq_len + t0 + b) * a.ldo + (size_t)h * V + j] = fmaf(u, par.z, par.y * mine);
+            for (int c = 0; c < NC; ++c) {
+                const float dkt = __shfl_sync(0xffffffffu, mine[c], lane & ~(SL - 1));
+                const float u = par.x * (sc[cw + c] - par.y * dkt);
+#pragma unroll
+                for (int n = 0; n < NR; ++n) S[c][n] = fmaf(kr[n], u, par.y * S[c][n]);
+                if (slice == 1 && j + c < V)
+                    a.o[(size_t)(s * a.seq_len + t0 + b) * a.ldo + (size_t)h * V + j + c] = fmaf(u, par.z, par.y * mine[c]);
+            }
         }
         __syncthreads();                           // the buffer is free for the copies after the next ones
     }
-    if (col) {
-        float* dst = st + (((size_t)((p0 + a.seq_len) & 1) * H + h) * V + j) * D;
+#pragma unroll
+    for (int c = 0; c < NC; ++c) {
+        if (j + c >= V) continue;
+        float* dst = st + (((size_t)((p0 + a.seq_len) & 1) * H + h) * V + j + c) * D;
 #pragma unroll
         for (int n = 0; n < NR; ++n) {
             const int i = slice * NR + n;
-            if (i < D) dst[i] = S[n];
+            if (i < D) dst[i] = S[c][n];
         }
     }
     if (h == 0 && tile == 0) {       // the convolutions' inputs of the last rows go to the ring
@@ -236,17 +253,17 @@ __global__ void __launch_bounds__(256) delta_rule_kernel(b200_delta_args a, int 
     }
 }
 
-template <int NR, int SL>
+template <int NR, int SL, int NC>
 static int launch_delta_rule(const b200_delta_args* a, cudaStream_t s) {
-    constexpr int COLS = 256 / SL;
+    constexpr int COLS = NC * 256 / SL;
     const int tb = a->seq_len < kDeltaBatch ? a->seq_len : kDeltaBatch;      // (a decode step stages one token)
     const size_t smem = (size_t)2 * tb * (2 * NR * SL + COLS + 4) * sizeof(float);
     if (smem > 48 * 1024)
-        B200_CUDA_CHECK(cudaFuncSetAttribute(delta_rule_kernel<NR, SL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        B200_CUDA_CHECK(cudaFuncSetAttribute(delta_rule_kernel<NR, SL, NC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     const int qk = a->kv_heads * a->dim;
     const int vec = (a->dim % 4 == 0 && a->ldw % 4 == 0 && qk % 4 == 0 && (reinterpret_cast<uintptr_t>(a->work) & 15) == 0) ? 1 : 0;
     dim3 grid(a->n_seq, a->heads, (a->vdim + COLS - 1) / COLS);
-    B200_CUDA_CHECK(launch(delta_rule_kernel<NR, SL>, grid, dim3(256), smem, s, a->pdl != 0, *a, vec, tb));
+    B200_CUDA_CHECK(launch(delta_rule_kernel<NR, SL, NC>, grid, dim3(256), smem, s, a->pdl != 0, *a, vec, tb));
     return B200_OK;
 }
 
@@ -280,9 +297,12 @@ extern "C" int b200_delta_rule(const b200_delta_args* a, void* stream) {
     if (!a->o) return fail(B200_EINVAL, "b200_delta_rule: o missing");
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     // (few rows per lane: the work of a token is a chain of dependent steps, so the more warps share it the better)
-    if (a->dim <= 64) return launch_delta_rule<4, 16>(a, s);
-    if (a->dim <= 128) return launch_delta_rule<4, 32>(a, s);
-    if (a->dim <= 256) return launch_delta_rule<8, 32>(a, s);
-    if (a->dim <= 512) return launch_delta_rule<16, 32>(a, s);
+    // a run of tokens: several columns per lane group (shared reads of k and q, independent chains); a decode step:
+    // as many blocks as possible, its time is the state's traffic
+    const bool run = a->seq_len > 1 && a->vdim >= 32;
+    if (a->dim <= 64) return run ? launch_delta_rule<4, 16, 2>(a, s) : launch_delta_rule<4, 16, 1>(a, s);
+    if (a->dim <= 128) return run ? launch_delta_rule<4, 32, 2>(a, s) : launch_delta_rule<4, 32, 1>(a, s);
+    if (a->dim <= 256) return run ? launch_delta_rule<8, 32, 2>(a, s) : launch_delta_rule<8, 32, 1>(a, s);
+    if (a->dim <= 512) return launch_delta_rule<16, 32, 1>(a, s);
     return fail(B200_ELIMIT, "b200_delta_rule: dim %d > 512", a->dim);
 }
