@@ -529,6 +529,66 @@ def test_long_prompts_in_large_chunks(name, dtype, tmp_root):
     mgr.close("long")
 
 
+@pytest.mark.parametrize("dtype", MODES, ids=["fp32", "bf16"])
+def test_long_decoding_with_a_large_cache(dtype, tmp_root):
+    """A cache of 1024 positions (decode attention divides every token's keys over 8 blocks; the shares' borders move with
+    the length) and 150 decode steps behind a 100-token prompt: state copies alternate 150 times, the key count passes
+    the 128-key borders of the shares."""
+    from petals_b200.models.config import resolve_config
+    from petals_b200.runtime.kv_cache import KVCacheManager
+    from petals_b200.runtime.layered_span import make_span
+    from petals_b200.weights.loader import load_span
+
+    name = "plain"
+    d = model(name, tmp_root)[2]
+    cfg = resolve_config(d)
+    w = load_span(d, cfg, 0, cfg.n_layers, need_embed=True, need_head=True, dtype=dtype, device=DEV)
+    span = make_span(cfg, w, DEV, dtype, kv_capacity=1024, max_batch=2, max_chunk=64)
+    assert span._sink_splits(1, cfg.layers[0].mixer)[0] == 8
+    mgr = KVCacheManager.for_span(cfg, 0, cfg.n_layers, dtype, DEV, default_max_length=1024)
+    toks = tokens_of(name, 250, 21)
+    want = oracle_logits(name, tmp_root, toks)
+    kv = mgr.allocate("far", 1024)
+    rows = [span.prefill(kv, ids=ids(toks[:100]), logits_at=[99])[0]]
+    for p in range(100, 250):
+        rows.append(span.decode([kv], ids=ids(toks[p:p + 1]))[0].clone())
+    assert rel_err(torch.cat(rows), want[99:]) < TOL[dtype]
+    mgr.close("far")
+
+
+@pytest.mark.parametrize("dtype", MODES, ids=["fp32", "bf16"])
+def test_two_spans_in_a_row_equal_the_whole_model(dtype, tmp_root):
+    """The model cut after its first layer, as two pipeline stages would hold it: the first span embeds and hands the fp32
+    stream on, the second one owns the recurrent layer's state and the last attention layer's cache and the head."""
+    from petals_b200.models.config import resolve_config
+    from petals_b200.runtime.kv_cache import KVCacheManager
+    from petals_b200.runtime.layered_span import make_span
+    from petals_b200.weights.loader import load_span
+
+    name = "plain"
+    d = model(name, tmp_root)[2]
+    cfg = resolve_config(d)
+    wa = load_span(d, cfg, 0, 1, need_embed=True, need_head=False, dtype=dtype, device=DEV)
+    wb = load_span(d, cfg, 1, 3, need_embed=False, need_head=True, dtype=dtype, device=DEV)
+    sa = make_span(cfg, wa, DEV, dtype, kv_capacity=128, max_batch=2, max_chunk=16)
+    sb = make_span(cfg, wb, DEV, dtype, kv_capacity=128, max_batch=2, max_chunk=16)
+    ma = KVCacheManager.for_span(cfg, 0, 1, dtype, DEV, default_max_length=128)
+    mb = KVCacheManager.for_span(cfg, 1, 3, dtype, DEV, default_max_length=128)
+    ka, kb = ma.allocate("s", 128), mb.allocate("s", 128)
+    assert ka.state is None and kb.state is not None and kb.state.numel() == cfg.state_elems(1, 3)
+    toks = tokens_of(name, 30, 22)
+    want = oracle_logits(name, tmp_root, toks)
+    h = sa.prefill(ka, ids=ids(toks[:21]))
+    assert h.dtype == torch.float32 and tuple(h.shape) == (21, cfg.hidden)
+    rows = [sb.prefill(kb, h_in=h, logits_at=list(range(21)))[0]]
+    for p in range(21, 30):
+        h1 = sa.decode([ka], ids=ids(toks[p:p + 1]))
+        rows.append(sb.decode([kb], h_in=h1)[0].clone())
+    assert rel_err(torch.cat(rows), want) < TOL[dtype]
+    with pytest.raises(ValueError):
+        resolve_config(model("mixed", tmp_root)[2]).check_span(2, 4)      # layer 2 blends with layer 1's values
+
+
 def test_a_freed_or_reset_session_is_clean_for_its_next_owner(tmp_root):
     """The same session name and the same bytes, used again for another request: neither cache rows nor matrices nor
     convolution inputs of the first one show (a recurrent layer reads no state at a sequence's first token)."""
@@ -607,6 +667,17 @@ def test_greedy_generation_through_the_engine(tmp_root):
     for p, o in zip(prompts, outs):
         assert o == O.greedy(cfg, w, p, 8)
     assert stats["decode_tok_per_s"] > 0
+
+
+def test_preset_with_random_weights_generates():
+    """``tiny-seledra``: no folder, weights drawn from the tensor names; two runs give the same tokens."""
+    from petals_b200.parallel.pipeline import PipelineEngine
+
+    eng = PipelineEngine("tiny-seledra", (), torch.bfloat16, torch.device(DEV), kv_capacity=64, max_sessions=2, max_chunk=16)
+    prompt = [torch.tensor([5, 9, 200, 17, 3])]
+    a, _ = eng.generate(prompt, max_new_tokens=6)
+    b, _ = eng.generate(prompt, max_new_tokens=6)
+    assert a == b and len(a[0]) == 6 and all(0 <= t < 512 for t in a[0])
 
 
 def test_sampled_generation_runs_on_the_device_sampler(tmp_root):
