@@ -256,8 +256,10 @@ __global__ void __launch_bounds__(256) delta_rule_kernel(b200_delta_args a, int 
 template <int NR, int SL, int NC>
 static int launch_delta_rule(const b200_delta_args* a, cudaStream_t s) {
     constexpr int COLS = NC * 256 / SL;
-    const int tb = a->seq_len < kDeltaBatch ? a->seq_len : kDeltaBatch;      // (a decode step stages one token)
-    const size_t smem = (size_t)2 * tb * (2 * NR * SL + COLS + 4) * sizeof(float);
+    const size_t per_token = (size_t)(2 * NR * SL + COLS + 4) * sizeof(float);
+    int tb = a->seq_len < kDeltaBatch ? a->seq_len : kDeltaBatch;            // (a decode step stages one token)
+    while (tb > 1 && 2 * tb * per_token > 200 * 1024) --tb;                  // (very long rows: fewer tokens per buffer)
+    const size_t smem = (size_t)2 * tb * per_token;
     if (smem > 48 * 1024)
         B200_CUDA_CHECK(cudaFuncSetAttribute(delta_rule_kernel<NR, SL, NC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     const int qk = a->kv_heads * a->dim;
@@ -304,5 +306,6 @@ extern "C" int b200_delta_rule(const b200_delta_args* a, void* stream) {
     if (a->dim <= 128) return run ? launch_delta_rule<4, 32, 2>(a, s) : launch_delta_rule<4, 32, 1>(a, s);
     if (a->dim <= 256) return run ? launch_delta_rule<8, 32, 2>(a, s) : launch_delta_rule<8, 32, 1>(a, s);
     if (a->dim <= 512) return launch_delta_rule<16, 32, 1>(a, s);
-    return fail(B200_ELIMIT, "b200_delta_rule: dim %d > 512", a->dim);
+    if (a->dim <= 1024) return launch_delta_rule<32, 32, 1>(a, s);
+    return fail(B200_ELIMIT, "b200_delta_rule: dim %d > 1024", a->dim);
 }

@@ -233,8 +233,13 @@ def sink_attn(a: SinkAttnArgs, splits: int = 1, scratch: Optional[torch.Tensor] 
 
 
 def sink_attn_prefill_fits(dim: int, vdim: int) -> bool:
-    """Can the tensor-core kernel take heads of these sizes?"""
-    return dim <= 512 and vdim <= 256
+    """Can the tensor-core kernel take heads of these sizes (its query tile, two key tiles and two value tiles must fit
+    into shared memory)?"""
+    if vdim > 256:
+        return False
+    dqp, nv = (dim + 15) // 16 * 16, (vdim + 7) // 8
+    nv = 4 if nv <= 4 else 8 if nv <= 8 else 16 if nv <= 16 else 32
+    return ((64 + 2 * 64) * (dqp + 8) + 2 * 64 * (nv * 8 + 8)) * 2 <= 200 * 1024
 
 
 def sink_attn_prefill(a: SinkAttnArgs) -> None:

@@ -46,6 +46,16 @@ CONFIGS = {
 }
 
 
+# one kind of mixer only, sizes that are multiples of nothing (the kernels' scalar paths), width that is no multiple of 8
+EXTRA_CONFIGS = {
+    "recurrent-only": {"architecture": "Seledra", "max_positions": 80, "norm": {"eps": 1e-5}, "residual_mult": 0.7, "vocab": 150,
+                       "width": 100, "layers": [_delta(3, 1, 18, 22, 2, ff=36), _delta(2, 2, 10, 6, 7)]},
+    "attention-only": {"architecture": "Seledra", "max_positions": 80, "norm": {"eps": 1e-5}, "residual_mult": 0.7, "vocab": 150,
+                       "width": 100, "layers": [_attn(3, 1, 20, 12, 0.2, True), _attn(2, 1, 6, 12, 0.4, True, ff=44),
+                                                _attn(4, 4, 10, 18, 0.3, False)]},
+}
+
+
 def _weights(cfg_dict, seed):
     from petals_b200.models.seledra import from_config_dict, tensor_shapes
 
@@ -84,7 +94,8 @@ def model(name, tmp_root):
     if name not in _MODELS:
         from petals_b200.weights.safetensors_io import save_file
 
-        cfg, w = CONFIGS[name], _weights(CONFIGS[name], 11 + len(name))
+        cfg = CONFIGS.get(name) or EXTRA_CONFIGS[name]
+        w = _weights(cfg, 11 + len(name))
         d = os.path.join(tmp_root, name)
         os.makedirs(d, exist_ok=True)
         json.dump(cfg, open(os.path.join(d, "config.json"), "w"))
@@ -129,7 +140,7 @@ def span_of(name, tmp_root, dtype, max_chunk=16):
 
 def tokens_of(name, n, seed=0):
     g = torch.Generator().manual_seed(300 + seed)
-    return torch.randint(0, CONFIGS[name]["vocab"], (n,), generator=g).tolist()
+    return torch.randint(0, (CONFIGS.get(name) or EXTRA_CONFIGS[name])["vocab"], (n,), generator=g).tolist()
 
 
 def row_errs(got, want):
@@ -332,7 +343,7 @@ def _delta_reference(x, conv_w, blog, alog, A_log, dt_bias, H, G, dk, dv, unit_e
     return work, read
 
 
-@pytest.mark.parametrize("H,G,dk,dv,taps", [(4, 2, 24, 40, 3), (3, 3, 20, 12, 1), (2, 1, 72, 136, 5), (2, 2, 130, 8, 2), (2, 1, 260, 20, 4)])
+@pytest.mark.parametrize("H,G,dk,dv,taps", [(4, 2, 24, 40, 3), (3, 3, 20, 12, 1), (2, 1, 72, 136, 5), (2, 2, 130, 8, 2), (2, 1, 260, 20, 4), (1, 1, 520, 8, 2)])
 @pytest.mark.parametrize("cuts", [(57,), (1, 1, 1, 2, 17, 16, 15, 4), (33, 24)], ids=["whole", "pieces", "two"])
 def test_delta_rule_in_pieces_carries_state_and_convolution_inputs(H, G, dk, dv, taps, cuts):
     """The recurrence over one sequence cut into launches of many sizes (one token, two, the kernel's 16-token batches
@@ -414,6 +425,23 @@ def test_prompt_logits_at_every_position(name, dtype, tmp_root):
     got = span.prefill(kv, ids=ids(toks), logits_at=list(range(len(toks))))[0]      # three chunks of 16, the last partial
     assert rel_err(got, oracle_logits(name, tmp_root, toks)) < TOL[dtype]
     mgr.close("p")
+
+
+@pytest.mark.parametrize("dtype", MODES, ids=["fp32", "bf16"])
+@pytest.mark.parametrize("name", sorted(EXTRA_CONFIGS))
+def test_models_with_one_kind_of_mixer_and_odd_sizes(name, dtype, tmp_root):
+    """No cache rows at all (only state), or no state at all (only rows); a 70-token prompt in 64-token chunks (the
+    tensor-core attention with sizes that rule out its 16-byte loads), then decoding."""
+    span, mgr = span_of(name, tmp_root, dtype, max_chunk=64)
+    toks = tokens_of(name, 78, 9)
+    want = oracle_logits(name, tmp_root, toks)
+    kv = mgr.allocate("x", 256)
+    assert (kv.state is None) == (name == "attention-only")
+    rows = [span.prefill(kv, ids=ids(toks[:70]), logits_at=list(range(70)))[0]]
+    for p in range(70, 78):
+        rows.append(span.decode([kv], ids=ids(toks[p:p + 1]))[0].clone())
+    assert rel_err(torch.cat(rows), want) < TOL[dtype]
+    mgr.close("x")
 
 
 def test_the_stream_after_every_layer(tmp_root):
