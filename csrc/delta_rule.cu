@@ -1,6 +1,7 @@
 // Gated delta rule behind short causal convolutions: a matrix state per head that decays, is corrected towards the
 // current value along the current key and is read with the query.  Everything here is fp32.
-//   prep  (one block per row):   convolutions + silu, unit-length q / k, beta and decay of every head
+//   prep  (one block per head and group of rows):   convolutions + silu, unit-length q / k, their dot product, beta
+//                                                   and decay of every head
 //   rule  (sequential in time):  S <- decay S;  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q
 // A sequence's state lives with its cache: two copies of the heads' matrices, column-major (a launch whose first token is at position
 // p0 reads copy p0 & 1 and writes copy (p0 + n) & 1, so a step that is run twice leaves the same state) and a ring of

@@ -1,6 +1,7 @@
 // Grouped-query softmax attention without rotation whose denominator carries a sink: normalisation of the projections
-// and the cache append (one block per token), then attention over the cached rows with fp32 scores, weights and sums
-// (one block per token, head and share of the keys; the shares of a decode step are merged by a second launch).
+// and the cache append (three blocks per token: queries, keys, values), then attention over the cached rows with fp32
+// scores, weights and sums (one block per token, head and share of the keys; the shares of a decode step are merged by a
+// second launch).
 // Cache planes keep all key (value) heads of a position side by side in one row.
 #include "common.h"
 #include "ptx.cuh"

@@ -490,7 +490,7 @@ int b200_xielu(const float* z, int32_t ld, const float* params, float lin, float
 /* Grouped-query softmax attention without rotation, with a sink in the denominator.
  * proj[t] (fp32 row of the fused projection): q [heads x dim] at q_off, k [kv_heads x dim] at k_off, v [kv_heads x vdim] at
  * v_off, one gate logit per head at g_off.
- * Step 1, b200_sink_attn_append (one block per token): adds `bias` (q | k | v order, may be NULL); RMS-norms the WHOLE q
+ * Step 1, b200_sink_attn_append (three blocks per token): adds `bias` (q | k | v order, may be NULL); RMS-norms the WHOLE q
  * row and the WHOLE k row (gains q_gain / k_gain, eps); folds scale * temp[h] into q (written back in place); divides every
  * value head by its root mean square over vdim (eps, no gain); vmix_mode 1: leaves the values in v_first[t]; 2: v <- (1 - l)
  * v + l v_first[t] with l = *vmix; then stores k and v as rows of the key / value planes at the token's position.
