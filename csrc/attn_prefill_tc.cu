@@ -547,15 +547,43 @@ static int launch_tc2(const AttnPrefillTc2Params& p, const CUtensorMap& mq, cons
 
 using namespace b200;
 
+// pos_stride / head_stride: elements between two positions / two kv heads of the cache planes (0, 0: one plane per head,
+// [n_kv][s_max][head_dim]); strided planes run on the TMA kernel only.
+static int attn_prefill_tc_impl(const void* q, void* out, const void* kcache, const void* vcache, int32_t T,
+                                int32_t n_heads, int32_t n_kv_heads, int32_t head_dim, int32_t s_max, int32_t ldq,
+                                int32_t ldo, int32_t pos0, float scale, int32_t dtype, int64_t pos_stride, int64_t head_stride,
+                                int32_t pdl, void* stream_);
+
 extern "C" int b200_attn_prefill_tc(const void* q, void* out, const void* kcache, const void* vcache, int32_t T,
                                     int32_t n_heads, int32_t n_kv_heads, int32_t head_dim, int32_t s_max, int32_t ldq,
                                     int32_t ldo, int32_t pos0, float scale, int32_t dtype, int32_t pdl, void* stream_) {
+    return attn_prefill_tc_impl(q, out, kcache, vcache, T, n_heads, n_kv_heads, head_dim, s_max, ldq, ldo, pos0, scale, dtype, 0, 0,
+                                pdl, stream_);
+}
+
+extern "C" int b200_attn_prefill_tc_rows(const void* q, void* out, const void* kcache, const void* vcache, int32_t T,
+                                         int32_t n_heads, int32_t n_kv_heads, int32_t head_dim, int32_t s_max, int32_t ldq,
+                                         int32_t ldo, int32_t pos0, float scale, int32_t dtype, int64_t pos_stride,
+                                         int64_t head_stride, int32_t pdl, void* stream_) {
+    if (pos_stride <= 0 || head_stride <= 0 || (pos_stride % 8) || (head_stride % 8) ||
+        (reinterpret_cast<uintptr_t>(kcache) & 15) || (reinterpret_cast<uintptr_t>(vcache) & 15) ||
+        (reinterpret_cast<uintptr_t>(q) & 15) || pos0 + T > s_max)
+        return fail(B200_EINVAL, "b200_attn_prefill_tc_rows: strides and addresses must be multiples of 16 bytes, pos0 + T <= s_max");
+    return attn_prefill_tc_impl(q, out, kcache, vcache, T, n_heads, n_kv_heads, head_dim, s_max, ldq, ldo, pos0, scale, dtype,
+                                pos_stride, head_stride, pdl, stream_);
+}
+
+static int attn_prefill_tc_impl(const void* q, void* out, const void* kcache, const void* vcache, int32_t T,
+                                int32_t n_heads, int32_t n_kv_heads, int32_t head_dim, int32_t s_max, int32_t ldq,
+                                int32_t ldo, int32_t pos0, float scale, int32_t dtype, int64_t pos_stride, int64_t head_stride,
+                                int32_t pdl, void* stream_) {
     if (!q || !out || !kcache || !vcache) return fail(B200_EINVAL, "b200_attn_prefill_tc: null pointer argument");
     if (head_dim != 128 && head_dim != 64) return fail(B200_EINVAL, "b200_attn_prefill_tc: unsupported head_dim=%d", head_dim);
     if (n_kv_heads <= 0 || n_heads % n_kv_heads) return fail(B200_EINVAL, "b200_attn_prefill_tc: bad head counts");
     if ((ldq % 8) || (ldo % 8)) return fail(B200_EINVAL, "b200_attn_prefill_tc: row strides must be multiples of 8 elements");
     static const int version = [] { const char* e = getenv("B200_ATTN_PREFILL_V"); return e ? atoi(e) : 2; }();
-    if (version != 1 && (reinterpret_cast<uintptr_t>(q) & 15) == 0 && pos0 + T <= s_max) {
+    const bool strided = pos_stride != 0;
+    if ((version != 1 || strided) && (reinterpret_cast<uintptr_t>(q) & 15) == 0 && pos0 + T <= s_max) {
         EncodeTiledFn enc = encode_tiled_fn();
         if (!enc) return fail(B200_ECUDA, "b200_attn_prefill_tc: cuTensorMapEncodeTiled is not available from the driver");
         const CUtensorMapDataType dt = (dtype == B200_BF16) ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
@@ -572,7 +600,8 @@ extern "C" int b200_attn_prefill_tc(const void* q, void* out, const void* kcache
         for (int i = 0; i < 2; ++i) {
             // bounded at the valid length: rows the cache has not been written to arrive as zeros
             const cuuint64_t dims[3] = {(cuuint64_t)head_dim, (cuuint64_t)(pos0 + T), (cuuint64_t)n_kv_heads};
-            const cuuint64_t strides[2] = {(cuuint64_t)head_dim * 2, (cuuint64_t)s_max * head_dim * 2};
+            const cuuint64_t strides[2] = {(cuuint64_t)(strided ? pos_stride : head_dim) * 2,
+                                           (cuuint64_t)(strided ? head_stride : (int64_t)s_max * head_dim) * 2};
             const cuuint32_t box[3] = {64, 128, 1};
             const CUresult r = enc(i == 0 ? &mk : &mv, dt, 3, const_cast<void*>(i == 0 ? kcache : vcache), dims, strides, box, estr,
                                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -595,6 +624,7 @@ extern "C" int b200_attn_prefill_tc(const void* q, void* out, const void* kcache
         return dtype == B200_BF16 ? launch_tc2<64, true>(p2, mq, mk, mv, grid2, pdl != 0, st)
                                   : launch_tc2<64, false>(p2, mq, mk, mv, grid2, pdl != 0, st);
     }
+    if (strided) return fail(B200_EINVAL, "b200_attn_prefill_tc_rows: arguments do not fit the TMA kernel");
     AttnPrefillTcParams p;
     p.q = static_cast<const uint16_t*>(q);
     p.out = static_cast<uint16_t*>(out);

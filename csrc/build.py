@@ -42,7 +42,7 @@ def _nvcc() -> str:
 # what that family launches (``build(unit_set=...)`` -> ops/libb200petals_<name>.so); the full library is every unit.
 UNIT_SETS = {
     "layered": ["common", "gemm", "gemm_prefill", "elementwise", "sampling", "stream32", "gemm_simt", "latent_attention",
-                "latent_attention_mma", "moe", "sink_attention", "sink_attention_mma", "delta_rule"],
+                "latent_attention_mma", "moe", "sink_attention", "sink_attention_mma", "delta_rule", "attn_prefill_tc"],
 }
 
 

@@ -49,7 +49,9 @@ __global__ void __launch_bounds__(256) sink_attn_append_kernel(b200_sink_attn_ar
         const float rstd = 1.0f / sqrtf(block_sum_256(ss, red) / (float)qn + a.eps);
         for (int c = tid; c < qn; c += 256) {
             const int h = c / a.dim;
-            q[c] = q[c] * rstd * a.q_gain[c] * (a.scale * (a.temp ? a.temp[h] : 1.0f));
+            const float v = q[c] * rstd * a.q_gain[c] * (a.scale * (a.temp ? a.temp[h] : 1.0f));
+            q[c] = v;
+            if (a.q16 && !f32) static_cast<uint16_t*>(a.q16)[(size_t)t * a.ldq16 + c] = float_to_h16(v, bf);
         }
         return;
     }

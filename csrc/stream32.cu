@@ -222,9 +222,32 @@ __global__ void __launch_bounds__(128) gated_head_norm_kernel(const float* __res
     }
 }
 
+// ------------------------------------------------------------------ one sigmoid gate per token and head, in place
+__global__ void __launch_bounds__(256) head_gate_kernel(void* __restrict__ x, int ldx, int dtype, const float* __restrict__ gate,
+                                                       int ldg, int T, int heads, int vdim) {
+    pdl_wait_prior_grid();
+    pdl_launch_dependents();
+    const size_t n = (size_t)T * heads * vdim;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        const int t = (int)(i / ((size_t)heads * vdim)), c = (int)(i - (size_t)t * heads * vdim), h = c / vdim;
+        const float g = 1.0f / (1.0f + expf(-gate[(size_t)t * ldg + h]));
+        store_elem(x, (size_t)t * ldx + c, load_elem(x, (size_t)t * ldx + c, dtype) * g, dtype);
+    }
+}
+
 }  // namespace b200
 
 using namespace b200;
+
+extern "C" int b200_head_gate(void* x, int32_t ldx, int32_t dtype, const float* gate, int32_t ldg, int32_t T, int32_t heads,
+                              int32_t vdim, int32_t pdl, void* stream) {
+    if (!x || !gate || T <= 0 || heads <= 0 || vdim <= 0) return fail(B200_EINVAL, "b200_head_gate: bad argument");
+    const size_t n = (size_t)T * heads * vdim;
+    const int blocks = (int)((n + 255) / 256 < 8192 ? (n + 255) / 256 : 8192);
+    B200_CUDA_CHECK(launch(head_gate_kernel, dim3(blocks), dim3(256), 0, static_cast<cudaStream_t>(stream), pdl != 0, x, ldx, dtype,
+                           gate, ldg, T, heads, vdim));
+    return B200_OK;
+}
 
 extern "C" int b200_embed_pos_f32(const void* ids, const void* table, const void* pos_table, int32_t table_dtype,
                                   const int32_t* pos, int32_t pos0, float* out, int32_t T, int32_t width, int32_t ldo,

@@ -74,7 +74,7 @@ class SinkAttnArgs(C.Structure):
                 ("kv_ptr_stride", i32), ("pos0", i32),
                 ("T", i32), ("heads", i32), ("kv_heads", i32), ("dim", i32), ("vdim", i32), ("row_elems", i32),
                 ("cache_dtype", i32), ("eps", f32), ("scale", f32), ("sink", f32), ("out", vp), ("ldo", i32),
-                ("out_dtype", i32), ("pdl", i32), ("reserved", i32)]
+                ("out_dtype", i32), ("pdl", i32), ("ldq16", i32), ("q16", vp)]
 
 
 class DeltaArgs(C.Structure):
@@ -96,6 +96,8 @@ PROTOTYPES = [
     ("b200_sink_attn_scratch_bytes", [i32, i32, i32, i32], i64),
     ("b200_delta_prep", [C.POINTER(DeltaArgs), vp], C.c_int),
     ("b200_delta_rule", [C.POINTER(DeltaArgs), vp], C.c_int),
+    ("b200_head_gate", [vp, i32, i32, vp, i32, i32, i32, i32, i32, vp], C.c_int),
+    ("b200_attn_prefill_tc_rows", [vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, f32, i32, i64, i64, i32, vp], C.c_int),
     ("b200_gated_head_norm", [vp, i32, vp, i32, vp, vp, i32, i32, i32, i32, i32, f32, i32, vp], C.c_int),
     ("b200_embed_f32", [vp, vp, i32, vp, i32, i32, i32, i32, i32, vp], C.c_int),
     ("b200_add_rms_norm", [C.POINTER(AddNormArgs), vp], C.c_int),

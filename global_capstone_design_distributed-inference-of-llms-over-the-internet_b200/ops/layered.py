@@ -200,7 +200,7 @@ def sink_attn_args(proj: torch.Tensor, *, q_off: int, k_off: int, v_off: int, g_
                    vmix: Optional[torch.Tensor] = None, v_first: Optional[torch.Tensor] = None, vmix_mode: int = 0,
                    k_cache: Optional[torch.Tensor] = None, v_cache: Optional[torch.Tensor] = None, pos0: int = 0,
                    kv_ptrs: Optional[torch.Tensor] = None, kv_ptr_stride: int = 0, pos: Optional[torch.Tensor] = None,
-                   out: Optional[torch.Tensor] = None, pdl: bool = False) -> SinkAttnArgs:
+                   out: Optional[torch.Tensor] = None, q16: Optional[torch.Tensor] = None, pdl: bool = False) -> SinkAttnArgs:
     assert proj.dtype == torch.float32
     for t in (bias, q_gain, k_gain, temp, vmix, v_first):
         assert t is None or t.dtype == torch.float32
@@ -217,7 +217,34 @@ def sink_attn_args(proj: torch.Tensor, *, q_off: int, k_off: int, v_off: int, g_
     a.ldo = out.stride(0) if out is not None else 0
     a.out_dtype = code(out.dtype) if out is not None else F32
     a.pdl = 1 if pdl else 0
+    if q16 is not None:
+        assert q16.dtype == cache_dtype and q16.dtype != torch.float32
+        a.q16, a.ldq16 = q16.data_ptr(), q16.stride(0)
     return a
+
+
+def head_gate(x: torch.Tensor, gate: torch.Tensor, heads: int, vdim: int, pdl: bool = False) -> None:
+    """x[t, h, :] *= sigmoid(gate[t, h]) in place; gate: fp32 [T, >= heads] view."""
+    assert gate.dtype == torch.float32
+    native.check(native.lib().b200_head_gate(x.data_ptr(), x.stride(0), code(x.dtype), gate.data_ptr(), gate.stride(0), x.shape[0],
+                                            heads, vdim, 1 if pdl else 0, _s()), "b200_head_gate")
+
+
+def attn_prefill_rows_fits(dim: int, vdim: int, row_elems: int) -> bool:
+    """Can the tcgen05 flash-attention kernel of the uniform families read these planes (equal key and value sizes of
+    64 or 128, 16-byte rows)?"""
+    return dim == vdim and dim in (64, 128) and row_elems % 8 == 0 and hasattr(native.lib(), "b200_attn_prefill_tc_rows")
+
+
+def attn_prefill_rows(q16: torch.Tensor, out: torch.Tensor, k_plane: torch.Tensor, v_plane: torch.Tensor, *, heads: int,
+                      kv_heads: int, dim: int, rows: int, pos0: int, scale: float, pdl: bool = False) -> None:
+    """Causal attention of a chunk on the tcgen05 kernel over planes [rows, row] that keep the heads of a position side
+    by side; query t sees rows 0 .. pos0 + t."""
+    assert q16.dtype == out.dtype == k_plane.dtype == v_plane.dtype and k_plane.stride(1) == 1
+    native.check(native.lib().b200_attn_prefill_tc_rows(
+        q16.data_ptr(), out.data_ptr(), k_plane.data_ptr(), v_plane.data_ptr(), q16.shape[0], heads, kv_heads, dim, rows,
+        q16.stride(0), out.stride(0), pos0, scale, code(out.dtype), k_plane.stride(0), dim, 1 if pdl else 0, _s()),
+        "b200_attn_prefill_tc_rows")
 
 
 def sink_attn_append(a: SinkAttnArgs) -> None:

@@ -164,7 +164,8 @@ class KVCacheManager:
         if len(src_idx) != len(sess) or any(not 0 <= h < len(sess) for h in src_idx):
             raise ValueError("hypo_ids must index into session_ids")
         need = {h for i, h in enumerate(src_idx) if h != i}
-        snap = {h: (sess[h].data[:, :, :, : sess[h].length].clone(), sess[h].length,
+        # (one row more than the length: layouts that keep a reserved row in front store position p in row p + 1)
+        snap = {h: (sess[h].data[:, :, :, : sess[h].length + 1].clone(), sess[h].length,
                     None if sess[h].state is None else sess[h].state.clone()) for h in need}
         for i, h in enumerate(src_idx):
             if h == i:
@@ -172,7 +173,8 @@ class KVCacheManager:
             data, length, state = snap[h]
             if length > sess[i].max_len:
                 raise ValueError("destination session is too small for the source hypothesis")
-            sess[i].data[:, :, :, :length].copy_(data)
+            n = min(data.shape[3], sess[i].max_len)
+            sess[i].data[:, :, :, :n].copy_(data[:, :, :, :n])
             if state is not None:
                 sess[i].state.copy_(state)
             sess[i].length = length

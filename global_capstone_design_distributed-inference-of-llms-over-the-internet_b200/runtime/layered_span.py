@@ -106,6 +106,11 @@ class LayeredSpan(NativeSpan):
         self.state_elems = cfg.state_elems(self.start, self.start + len(specs))
         self.state_slot = self.n_slots if self.state_elems else None
         state_off = cfg.state_offsets(self.start, self.start + len(specs)) if self.state_elems else {}
+        # Attention with a sink keeps row 0 of its planes at zero and stores position p in row p + 1: a key of score 0
+        # without a value IS the sink, so a plain causal softmax over rows 0 .. p + 1 (the tcgen05 kernel of the uniform
+        # families) gives the same weights; this span's own kernels get the planes from row 1 on and start their
+        # running sums at the sink instead.  A session therefore holds one token less than its rows.
+        self.sink_row = 1 if any(isinstance(S.mixer, SD.SinkAttentionSpec) for S in specs) else 0
         self.gain_offset = float(cfg.norm_gain_offset)
         self.residual_mult = float(cfg.residual_mult)
         with torch.cuda.device(self.device):
@@ -191,6 +196,9 @@ class LayeredSpan(NativeSpan):
                 self.delta_o = f32(Tm, max(d.v_size for d in deltas))
             vm = [P["spec"].mixer for P in self.layers if getattr(P["spec"].mixer, "v_mix", False)]
             self.v_first = f32(Tm, max(v.v_size for v in vm)) if vm else None
+            tcq = [P["spec"].mixer for P in self.layers if isinstance(P["spec"].mixer, SD.SinkAttentionSpec) and not ex
+                   and L.attn_prefill_rows_fits(P["spec"].mixer.dim, P["spec"].mixer.vdim, self.row_elems)]
+            self.q16 = act(Tm, max(q.q_size for q in tcq)) if tcq else None      # queries for the TMA-fed attention kernel
             moe = [P["spec"].mlp for P in self.layers if isinstance(P["spec"].mlp, Z.MoESpec)]
             if moe:
                 top, ne, ffe = max(e.top for e in moe), max(e.experts for e in moe), max(e.ff for e in moe)
@@ -230,6 +238,8 @@ class LayeredSpan(NativeSpan):
 
     def _ptr_column(self, kv: SessionKV, nl: int) -> torch.Tensor:
         col = super()._ptr_column(kv, nl)
+        if self.sink_row:             # this span's decode kernels see the planes from row 1 on (row 0 is the sink's)
+            col[:self.n_slots] += self.sink_row * self.row_elems * kv.data.element_size()
         if self.state_elems:          # last row: where the session's recurrent state lives
             if kv.state is None or kv.state.numel() < self.state_elems:
                 raise ValueError(f"session {kv.session_id} carries no state for this span's recurrent layers")
@@ -389,14 +399,25 @@ class LayeredSpan(NativeSpan):
                   dim=m.dim, vdim=m.vdim, row_elems=self.row_elems, cache_dtype=self.dtype, eps=self.cfg.norm_eps,
                   scale=m.scale, sink=m.sink, T=T, bias=P["qkv_b"], q_gain=P["q_norm_w"], k_gain=P["k_norm_w"], temp=P["temp"],
                   vmix=P["vmix"], v_first=self.v_first, vmix_mode=P["vmix_mode"], out=cat, pdl=self.pdl)
-        if "kv" in where:      # one session: its planes, consecutive positions
+        portion = "kv" in where and not self.exact and T >= TC_ATTN_MIN_TOKENS
+        tcgen05 = portion and self.q16 is not None and L.attn_prefill_rows_fits(m.dim, m.vdim, self.row_elems)
+        if "kv" in where:      # one session: its planes (from the first token's row on), consecutive positions
             kv = where["kv"]
-            kw.update(k_cache=kv.plane(P["slot"], 0), v_cache=kv.plane(P["slot"], 1), pos0=where["pos0"])
+            kw.update(k_cache=kv.plane(P["slot"], 0)[self.sink_row:], v_cache=kv.plane(P["slot"], 1)[self.sink_row:],
+                      pos0=where["pos0"])
         else:                  # a batch of sessions: staged pointer table and positions
             kw.update(kv_ptrs=self.kv_ptrs[P["slot"]], kv_ptr_stride=2, pos=self.pos)
+        if tcgen05:
+            kw.update(q16=self.q16[:T])
         a = L.sink_attn_args(proj, **kw)
         L.sink_attn_append(a)
-        if "kv" in where and not self.exact and T >= TC_ATTN_MIN_TOKENS and L.sink_attn_prefill_fits(m.dim, m.vdim):
+        if tcgen05:            # equal key / value sizes of 64 or 128: the uniform families' kernel over rows 0 .. p + 1, then the gate
+            L.attn_prefill_rows(self.q16[:T, :m.q_size], cat, kv.plane(P["slot"], 0), kv.plane(P["slot"], 1), heads=m.heads,
+                                kv_heads=m.kv_heads, dim=m.dim, rows=kv.max_len, pos0=where["pos0"] + self.sink_row, scale=1.0,
+                                pdl=self.pdl)
+            L.head_gate(cat, proj[:, P["g_off"]:], m.heads, m.vdim, pdl=self.pdl)
+            self._count()
+        elif portion and L.sink_attn_prefill_fits(m.dim, m.vdim):
             L.sink_attn_prefill(a)
         else:
             L.sink_attn(a, *self._sink_splits(T, m))
@@ -522,8 +543,8 @@ class LayeredSpan(NativeSpan):
         self._prestaged = None
         pos0 = kv.length if pos0 is None else pos0
         T = ids.shape[0] if h_in is None else h_in.shape[0]
-        if pos0 + T > kv.max_len:
-            raise ValueError(f"session {kv.session_id}: {pos0}+{T} tokens exceed max_length {kv.max_len}")
+        if pos0 + T > kv.max_len - self.sink_row:
+            raise ValueError(f"session {kv.session_id}: {pos0}+{T} tokens exceed max_length {kv.max_len - self.sink_row}")
         if kv.max_len != self.kv_capacity or kv.data.shape[0] != self.n_slots or kv.data.shape[-1] != self.row_elems or \
                 kv.data.shape[1] != self.cache_planes or (self.state_elems and (kv.state is None or kv.state.numel() < self.state_elems)):
             raise ValueError(f"session cache {tuple(kv.data.shape)} does not fit this span "

@@ -265,6 +265,7 @@ class NativeSpan:
     def _count(self, n: int = 1) -> None:
         self.kernel_launches += n
 
+    sink_row = 0       # rows at the head of every cache plane that hold no token (spans whose attention keeps a sink row)
     tp = None          # TPWorkspace when this span is one shard of a tensor-parallel group
     tp_mode = None     # "fused" | "nccl"
     tp_group = None
@@ -537,8 +538,8 @@ class NativeSpan:
             self._ptr_key = key
             n_copy = host.numel()                 # positions and pointers travel in the same copy
         for b, kv in enumerate(kvs):
-            if kv.length + 1 > kv.max_len:
-                raise ValueError(f"session {kv.session_id}: max_length {kv.max_len} reached")
+            if kv.length + 1 > kv.max_len - self.sink_row:
+                raise ValueError(f"session {kv.session_id}: max_length {kv.max_len - self.sink_row} reached")
             host[b] = kv.length
             host[self.max_batch + 1 + b] = getattr(kv, "sampler_row", 0) or 0
         self._seq_host = self._seq_host % 1000000 + 1        # a new step number for every staged step (never 0)
@@ -672,8 +673,8 @@ class NativeSpan:
         self._prestaged = None
         B = len(kvs)
         for kv in kvs:
-            if kv.length + n_steps > kv.max_len:
-                raise ValueError(f"session {kv.session_id}: {kv.length}+{n_steps} exceeds max_length {kv.max_len}")
+            if kv.length + n_steps > kv.max_len - self.sink_row:
+                raise ValueError(f"session {kv.session_id}: {kv.length}+{n_steps} exceeds max_length {kv.max_len - self.sink_row}")
         self._stage_ptrs(kvs)
         key = ("loop", B)
         g = self._graphs.get(key)

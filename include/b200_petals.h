@@ -261,6 +261,12 @@ int b200_attn_prefill(const void* q, void* out, const void* kcache, const void* 
 int b200_attn_prefill_tc(const void* q, void* out, const void* kcache, const void* vcache, int32_t T, int32_t n_heads,
                          int32_t n_kv_heads, int32_t head_dim, int32_t s_max, int32_t ldq, int32_t ldo, int32_t pos0,
                          float scale, int32_t dtype, int32_t pdl, void* stream);
+/* The same kernel over cache planes with any element strides between positions (pos_stride) and between kv heads
+ * (head_stride), e.g. planes that keep all heads of a position side by side: pos_stride = row, head_stride = head_dim.
+ * Strides and addresses must be multiples of 16 bytes. */
+int b200_attn_prefill_tc_rows(const void* q, void* out, const void* kcache, const void* vcache, int32_t T, int32_t n_heads,
+                              int32_t n_kv_heads, int32_t head_dim, int32_t s_max, int32_t ldq, int32_t ldo, int32_t pos0,
+                              float scale, int32_t dtype, int64_t pos_stride, int64_t head_stride, int32_t pdl, void* stream);
 
 /* ----------------------------------------------------------- elementwise --
  * Embedding gather (+ learned positions for GPT-2): src/llama_partition.py:107.
@@ -519,7 +525,9 @@ typedef struct b200_sink_attn_args {
     float eps, scale, sink;
     void* out;
     int32_t ldo, out_dtype;
-    int32_t pdl, reserved;
+    int32_t pdl, ldq16;
+    void* q16;            /* optional: b200_sink_attn_append also leaves the finished queries here, in the cache's 16-bit type
+                             ([T, heads * dim], row stride ldq16), for a kernel that reads its queries by TMA */
 } b200_sink_attn_args;
 int b200_sink_attn_append(const b200_sink_attn_args* args, void* stream);
 int b200_sink_attn(const b200_sink_attn_args* args, int32_t splits, float* scratch, void* stream);
@@ -564,6 +572,10 @@ typedef struct b200_delta_args {
 } b200_delta_args;
 int b200_delta_prep(const b200_delta_args* args, void* stream);
 int b200_delta_rule(const b200_delta_args* args, void* stream);
+
+/* x[t, h, :] *= sigmoid(gate[t, h]) in place; x: 16-bit or fp32 [T, heads * vdim] (row stride ldx), gate: fp32 (row stride ldg). */
+int b200_head_gate(void* x, int32_t ldx, int32_t dtype, const float* gate, int32_t ldg, int32_t T, int32_t heads, int32_t vdim,
+                   int32_t pdl, void* stream);
 
 /* Gated RMS norm per head: out[t, h, :] = o[t, h, :] / sqrt(mean(o^2) + eps) * gain[:] * silu(gate[t, h, :]).
  * o: fp32 [T, heads * vdim] (ldo); gate: fp32 rows (ldg) holding heads * vdim logits; gain: fp32 [vdim] shared by the

@@ -56,7 +56,7 @@ class TraceReplayer:
         _ensure_library(self.cfg)
         from petals_b200.parallel.pipeline import PipelineEngine
 
-        cap = max(64, (int(max_tokens) + 63) // 64 * 64)
+        cap = max(64, (int(max_tokens) + 1 + 63) // 64 * 64)       # (+ 1: a family may keep one row of its planes for itself)
         self.eng = PipelineEngine(model, (), dtype, self.device, kv_capacity=cap, max_sessions=MAX_DECODE_BATCH,
                                   max_chunk=512, cfg=self.cfg)
         self.span, self.kv = self.eng.span, self.eng.kv

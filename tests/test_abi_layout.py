@@ -25,7 +25,7 @@ int main(void) {
     printf("hop %zu %zu %zu\n", sizeof(b200_hop_args), offsetof(b200_hop_args, counter), offsetof(b200_hop_args, pdl));
     printf("addnorm %zu %zu %zu\n", sizeof(b200_add_norm_args), offsetof(b200_add_norm_args, eps), offsetof(b200_add_norm_args, add_scale));
     printf("sink %zu %zu %zu %zu %zu\n", sizeof(b200_sink_attn_args), offsetof(b200_sink_attn_args, bias),
-           offsetof(b200_sink_attn_args, k_cache), offsetof(b200_sink_attn_args, T), offsetof(b200_sink_attn_args, out));
+           offsetof(b200_sink_attn_args, k_cache), offsetof(b200_sink_attn_args, T), offsetof(b200_sink_attn_args, q16));
     printf("delta %zu %zu %zu %zu %zu\n", sizeof(b200_delta_args), offsetof(b200_delta_args, conv_w),
            offsetof(b200_delta_args, state_off), offsetof(b200_delta_args, n_seq), offsetof(b200_delta_args, o));
     return 0;
@@ -54,7 +54,7 @@ def test_ctypes_structs_match_the_header(tmp_path):
     assert out["hop"] == [ctypes.sizeof(HopArgs), HopArgs.counter.offset, HopArgs.pdl.offset]
     assert out["addnorm"] == [ctypes.sizeof(AddNormArgs), AddNormArgs.eps.offset, AddNormArgs.add_scale.offset]
     assert out["sink"] == [ctypes.sizeof(SinkAttnArgs), SinkAttnArgs.bias.offset, SinkAttnArgs.k_cache.offset,
-                           SinkAttnArgs.T.offset, SinkAttnArgs.out.offset]
+                           SinkAttnArgs.T.offset, SinkAttnArgs.q16.offset]
     assert out["delta"] == [ctypes.sizeof(DeltaArgs), DeltaArgs.conv_w.offset, DeltaArgs.state_off.offset,
                             DeltaArgs.n_seq.offset, DeltaArgs.o.offset]
 

@@ -53,6 +53,10 @@ EXTRA_CONFIGS = {
     "attention-only": {"architecture": "Seledra", "max_positions": 80, "norm": {"eps": 1e-5}, "residual_mult": 0.7, "vocab": 150,
                        "width": 100, "layers": [_attn(3, 1, 20, 12, 0.2, True), _attn(2, 1, 6, 12, 0.4, True, ff=44),
                                                 _attn(4, 4, 10, 18, 0.3, False)]},
+    # equal key and value sizes of 64 and 128: prompt portions of the 16-bit mode run on the tcgen05 attention kernel
+    "square": {"architecture": "Seledra", "max_positions": 200, "norm": {"eps": 1e-5}, "residual_mult": 0.6, "vocab": 190,
+               "width": 128, "layers": [_attn(4, 2, 64, 64, 0.12, True, ff=96), _delta(2, 1, 32, 48, 4),
+                                        _attn(2, 1, 128, 128, 0.08, False), _attn(2, 2, 64, 64, 0.12, True, ff=64)]},
 }
 
 
@@ -431,14 +435,18 @@ def test_prompt_logits_at_every_position(name, dtype, tmp_root):
 @pytest.mark.parametrize("name", sorted(EXTRA_CONFIGS))
 def test_models_with_one_kind_of_mixer_and_odd_sizes(name, dtype, tmp_root):
     """No cache rows at all (only state), or no state at all (only rows); a 70-token prompt in 64-token chunks (the
-    tensor-core attention with sizes that rule out its 16-byte loads), then decoding."""
+    tensor-core attention with sizes that rule out its 16-byte loads), then decoding.  And a model whose attention
+    layers have equal key and value sizes of 64 / 128 (their portions run on the tcgen05 kernel over the planes with
+    the sink's zero row in front, the gate applied behind it)."""
     span, mgr = span_of(name, tmp_root, dtype, max_chunk=64)
-    toks = tokens_of(name, 78, 9)
+    n = 158 if name == "square" else 78          # (square: a second full chunk that starts mid-session)
+    toks = tokens_of(name, n, 9)
     want = oracle_logits(name, tmp_root, toks)
     kv = mgr.allocate("x", 256)
     assert (kv.state is None) == (name == "attention-only")
-    rows = [span.prefill(kv, ids=ids(toks[:70]), logits_at=list(range(70)))[0]]
-    for p in range(70, 78):
+    assert (span.q16 is not None) == (name == "square" and dtype != torch.float32)
+    rows = [span.prefill(kv, ids=ids(toks[:n - 8]), logits_at=list(range(n - 8)))[0]]
+    for p in range(n - 8, n):
         rows.append(span.decode([kv], ids=ids(toks[p:p + 1]))[0].clone())
     assert rel_err(torch.cat(rows), want) < TOL[dtype]
     mgr.close("x")
@@ -615,6 +623,22 @@ def test_two_spans_in_a_row_equal_the_whole_model(dtype, tmp_root):
     assert rel_err(torch.cat(rows), want) < TOL[dtype]
     with pytest.raises(ValueError):
         resolve_config(model("mixed", tmp_root)[2]).check_span(2, 4)      # layer 2 blends with layer 1's values
+
+
+def test_a_session_holds_one_token_less_than_its_rows(tmp_root):
+    """Attention with a sink keeps row 0 of its planes for the sink: 127 tokens fit into 128 rows, the 128th is refused;
+    the last rows are read correctly."""
+    name, dtype = "mixed", torch.float32
+    span, mgr = span_of(name, tmp_root, dtype)
+    toks = tokens_of(name, 128, 13)
+    kv = mgr.allocate("full", 128)
+    span.prefill(kv, ids=ids(toks[:125]))
+    rows = [span.decode([kv], ids=ids(toks[p:p + 1]))[0].clone() for p in (125, 126)]
+    assert rel_err(torch.cat(rows), oracle_logits(name, tmp_root, toks[:127])[125:]) < TOL[dtype]
+    assert float(kv.data[:, :, :, 0].abs().max()) == 0.0
+    with pytest.raises(ValueError):
+        span.decode([kv], ids=ids(toks[127:128]))
+    mgr.close("full")
 
 
 def test_a_freed_or_reset_session_is_clean_for_its_next_owner(tmp_root):
