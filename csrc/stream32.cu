@@ -224,10 +224,26 @@ __global__ void __launch_bounds__(128) gated_head_norm_kernel(const float* __res
 
 // ------------------------------------------------------------------ one sigmoid gate per token and head, in place
 __global__ void __launch_bounds__(256) head_gate_kernel(void* __restrict__ x, int ldx, int dtype, const float* __restrict__ gate,
-                                                       int ldg, int T, int heads, int vdim) {
+                                                       int ldg, int T, int heads, int vdim, int vec) {
     pdl_wait_prior_grid();
     pdl_launch_dependents();
     const size_t n = (size_t)T * heads * vdim;
+    if (vec) {      // 16-bit values, eight per thread (they share a head)
+        const int per_row = heads * vdim / 8, bf = dtype == B200_BF16;
+        for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n / 8; i += (size_t)gridDim.x * blockDim.x) {
+            const int t = (int)(i / per_row), c = (int)(i - (size_t)t * per_row) * 8, h = c / vdim;
+            const float g = 1.0f / (1.0f + expf(-gate[(size_t)t * ldg + h]));
+            uint4* p = reinterpret_cast<uint4*>(static_cast<uint16_t*>(x) + (size_t)t * ldx + c);
+            uint4 v = *p;
+            uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int k = 0; k < 4; ++k)
+                w[k] = (uint32_t)float_to_h16(h16_to_float((uint16_t)(w[k] & 0xffff), bf) * g, bf) |
+                       ((uint32_t)float_to_h16(h16_to_float((uint16_t)(w[k] >> 16), bf) * g, bf) << 16);
+            *p = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+        return;
+    }
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
         const int t = (int)(i / ((size_t)heads * vdim)), c = (int)(i - (size_t)t * heads * vdim), h = c / vdim;
         const float g = 1.0f / (1.0f + expf(-gate[(size_t)t * ldg + h]));
@@ -242,10 +258,11 @@ using namespace b200;
 extern "C" int b200_head_gate(void* x, int32_t ldx, int32_t dtype, const float* gate, int32_t ldg, int32_t T, int32_t heads,
                               int32_t vdim, int32_t pdl, void* stream) {
     if (!x || !gate || T <= 0 || heads <= 0 || vdim <= 0) return fail(B200_EINVAL, "b200_head_gate: bad argument");
-    const size_t n = (size_t)T * heads * vdim;
+    const int vec = (dtype != B200_F32 && vdim % 8 == 0 && ldx % 8 == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0) ? 1 : 0;
+    const size_t n = (size_t)T * heads * vdim / (vec ? 8 : 1);
     const int blocks = (int)((n + 255) / 256 < 8192 ? (n + 255) / 256 : 8192);
     B200_CUDA_CHECK(launch(head_gate_kernel, dim3(blocks), dim3(256), 0, static_cast<cudaStream_t>(stream), pdl != 0, x, ldx, dtype,
-                           gate, ldg, T, heads, vdim));
+                           gate, ldg, T, heads, vdim, vec));
     return B200_OK;
 }
 

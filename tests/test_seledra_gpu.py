@@ -218,6 +218,21 @@ def test_gated_norm_per_head():
     assert torch.allclose(out.cpu().double().view(T, H, V), want, atol=1e-5)
 
 
+@pytest.mark.parametrize("dt,V", [(torch.bfloat16, 64), (torch.bfloat16, 12), (torch.float32, 20)])
+def test_gate_per_head_in_place(dt, V):
+    from petals_b200.ops import layered as L
+
+    g = torch.Generator().manual_seed(4)
+    T, H = 7, 3
+    x = torch.randn(T, H * V + 8, generator=g).to(dt)
+    gate = torch.randn(T, H + 2, generator=g)
+    xd = x.clone().to(DEV)
+    L.head_gate(xd, gate.to(DEV)[:, 1:], H, V)
+    want = x.float()[:, :H * V].view(T, H, V) * torch.sigmoid(gate[:, 1:1 + H])[..., None]
+    assert torch.allclose(xd[:, :H * V].float().cpu().view(T, H, V), want, atol=2e-2 if dt == torch.bfloat16 else 1e-6, rtol=1e-2)
+    assert torch.equal(xd[:, H * V:].cpu(), x[:, H * V:])
+
+
 def _sink_reference(q, k, v, qpos, H, G, sink):
     """q [T, H, dk] (scale folded in), k [S, G, dk], v [S, G, dv] float64 -> [T, H, dv]."""
     out = torch.zeros(q.shape[0], H, v.shape[-1], dtype=F64)
