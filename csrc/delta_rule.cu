@@ -1,6 +1,6 @@
 // Gated delta rule behind short causal convolutions: a matrix state per head that decays, is corrected towards the
 // current value along the current key and is read with the query.  Everything here is fp32.
-//   prep  (one block per head and group of rows):   convolutions + silu, unit-length q / k, their dot product, beta
+//   prep  (one warp or block per head and rows):    convolutions + silu, unit-length q / k, their dot product, beta
 //                                                   and decay of every head
 //   rule  (sequential in time):  S <- decay S;  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q
 // A sequence's state lives with its cache: two copies of the heads' matrices, column-major (a launch whose first token is at position
@@ -21,19 +21,25 @@ __device__ __forceinline__ float softplus32(float x) { return fmaxf(x, 0.f) + lo
 // ------------------------------------------------------------------ prep
 // One block per (group of consecutive rows of a sequence, unit); a unit is a query head with its key head (convolved,
 // activated, made unit vectors, and their dot product, which the read-out needs) or a value head (convolved and
-// activated); the block of unit 0 also evaluates beta and the decay of every head.
-__global__ void __launch_bounds__(128) delta_prep_kernel(b200_delta_args a, int rows_per_block) {
+// activated); the block of unit 0 also evaluates beta and the decay of every head.  Runs of tokens take one WARP per
+// unit (the step is bound by instruction issue there: no barrier and no shared-memory reduction per row), a decode step
+// four warps (its time is the chain of one row's loads).
+template <int kPrepThreads>
+__global__ void __launch_bounds__(kPrepThreads) delta_prep_kernel(b200_delta_args a, int rows_per_block) {
     extern __shared__ float y[];                   // pair: q [dim] | k [dim]; value head: [vdim]
     __shared__ float red[3][4];
     pdl_wait_prior_grid();
     pdl_launch_dependents();
-    const int unit = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int unit = blockIdx.y, tid = threadIdx.x;
     const int groups = (a.seq_len + rows_per_block - 1) / rows_per_block;
     const int s = blockIdx.x / groups, i0 = (blockIdx.x - s * groups) * rows_per_block;
     const int i1 = i0 + rows_per_block < a.seq_len ? i0 + rows_per_block : a.seq_len;
     for (int i = i0; i < i1; ++i) {
     const int r = s * a.seq_len + i;
-    __syncthreads();                               // y and red are free again
+    if (kPrepThreads > 32)
+        __syncthreads();                           // red is free again
+    else
+        __syncwarp();
     const int p = (a.pos ? a.pos[s] : a.pos0) + i;
     const int D = a.dim, V = a.vdim, G = a.kv_heads, H = a.heads;
     const int qk = G * D, C = 2 * qk + H * V, taps = a.taps;
@@ -60,19 +66,19 @@ __global__ void __launch_bounds__(128) delta_prep_kernel(b200_delta_args a, int 
     };
     if (unit == 0) {
         const float* rr = a.proj + (size_t)r * a.ldp;
-        for (int h = tid; h < H; h += 128) {
+        for (int h = tid; h < H; h += kPrepThreads) {
             out[C + h] = 1.0f / (1.0f + expf(-rr[a.b_off + h]));
             out[C + H + h] = expf(-expf(a.A_log[h]) * softplus32(rr[a.a_off + h] + a.dt_bias[h]));
         }
     }
     if (unit >= G) {                               // a value head
         const int h = unit - G;
-        for (int d = tid; d < V; d += 128) out[2 * qk + h * V + d] = conv(2 * qk + h * V + d);
+        for (int d = tid; d < V; d += kPrepThreads) out[2 * qk + h * V + d] = conv(2 * qk + h * V + d);
         continue;
     }
     const int g = unit;
     float sq = 0.f, sk = 0.f;
-    for (int d = tid; d < D; d += 128) {
+    for (int d = tid; d < D; d += kPrepThreads) {
         const float qv = conv(g * D + d), kv = conv(qk + g * D + d);
         y[d] = qv;
         y[D + d] = kv;
@@ -80,20 +86,22 @@ __global__ void __launch_bounds__(128) delta_prep_kernel(b200_delta_args a, int 
         sk = fmaf(kv, kv, sk);
     }
     float dot = 0.f;
-    for (int d = tid; d < D; d += 128) dot = fmaf(y[d], y[D + d], dot);   // (each thread reads what it wrote)
+    for (int d = tid; d < D; d += kPrepThreads) dot = fmaf(y[d], y[D + d], dot);   // (each thread reads what it wrote)
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
         sq += __shfl_xor_sync(0xffffffffu, sq, o);
         sk += __shfl_xor_sync(0xffffffffu, sk, o);
         dot += __shfl_xor_sync(0xffffffffu, dot, o);
     }
-    if (lane == 0) red[0][warp] = sq, red[1][warp] = sk, red[2][warp] = dot;
-    __syncthreads();
-    sq = (red[0][0] + red[0][1]) + (red[0][2] + red[0][3]);
-    sk = (red[1][0] + red[1][1]) + (red[1][2] + red[1][3]);
-    dot = (red[2][0] + red[2][1]) + (red[2][2] + red[2][3]);
+    if (kPrepThreads > 32) {
+        if ((tid & 31) == 0) red[0][tid >> 5] = sq, red[1][tid >> 5] = sk, red[2][tid >> 5] = dot;
+        __syncthreads();
+        sq = sk = dot = 0.f;
+#pragma unroll
+        for (int w = 0; w < kPrepThreads / 32; ++w) sq += red[0][w], sk += red[1][w], dot += red[2][w];
+    }
     const float fq = (1.0f / sqrtf(sq + a.unit_eps)) * rsqrtf((float)D), fk = 1.0f / sqrtf(sk + a.unit_eps);
-    for (int d = tid; d < D; d += 128) {
+    for (int d = tid; d < D; d += kPrepThreads) {
         out[g * D + d] = y[d] * fq;
         out[qk + g * D + d] = y[D + d] * fk;
     }
@@ -290,8 +298,11 @@ extern "C" int b200_delta_prep(const b200_delta_args* a, void* stream) {
     const size_t smem = (size_t)(2 * a->dim > a->vdim ? 2 * a->dim : a->vdim) * sizeof(float);
     if (smem > 48 * 1024) return fail(B200_ELIMIT, "b200_delta_prep: dim %d exceeds shared memory", a->dim);
     const int rpb = a->seq_len >= 64 ? 8 : 1;
-    B200_CUDA_CHECK(launch(delta_prep_kernel, dim3(a->n_seq * ((a->seq_len + rpb - 1) / rpb), a->kv_heads + a->heads), dim3(128),
-                           smem, static_cast<cudaStream_t>(stream), a->pdl != 0, *a, rpb));
+    const dim3 grid(a->n_seq * ((a->seq_len + rpb - 1) / rpb), a->kv_heads + a->heads);
+    if (rpb > 1)
+        B200_CUDA_CHECK(launch(delta_prep_kernel<32>, grid, dim3(32), smem, static_cast<cudaStream_t>(stream), a->pdl != 0, *a, rpb));
+    else
+        B200_CUDA_CHECK(launch(delta_prep_kernel<128>, grid, dim3(128), smem, static_cast<cudaStream_t>(stream), a->pdl != 0, *a, rpb));
     return B200_OK;
 }
 

@@ -544,7 +544,7 @@ int b200_sink_attn_prefill(const b200_sink_attn_args* args, void* stream);
  * A sequence's state (fp32, at state_ptrs ? state_ptrs[s * state_ptr_stride] : state, plus state_off elements):
  * [2][heads][vdim][dim] matrices (column-major) - a launch whose first token is at p0 reads copy p0 & 1 (zeros when p0 = 0) and writes copy
  * (p0 + seq_len) & 1 - followed by a ring [taps][channels] of convolution inputs, slot = position mod taps.
- * Step 1, b200_delta_prep (one block per row and head): y_c = silu(sum_b w[c][taps-1-b] x_c(p - b)), inputs before the sequence's
+ * Step 1, b200_delta_prep (one warp or block per head and group of rows): y_c = silu(sum_b w[c][taps-1-b] x_c(p - b)), inputs before the sequence's
  * start are zero, inputs before the launch's first row come from the ring; q and k heads become unit vectors
  * x / sqrt(sum x^2 + unit_eps), q also times dim^-1/2; beta = sigmoid(.), decay = exp(-exp(A_log) softplus(. + dt_bias)).
  * work[r] = [q | k | v | beta | decay | k.q per key head] (fp32, row stride ldw >= channels + 2 heads + kv_heads).
